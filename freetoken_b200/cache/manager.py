@@ -89,6 +89,25 @@ class PagedKVNeed(PerTokenNeed):
 
 
 @dataclass(frozen=True)
+class PagedKeyNeed(PerTokenNeed):
+    """ONE tensor per token and KV head: keys that are also the values, or a latent
+    vector from which keys and values are made.  Pages are ``[pages, kv_heads, page_size,
+    head_dim]``; the attention kernels read them as keys and, a second time, as values."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+    kind: str = "paged_key"
+    page_axis = 0
+
+    def layout(self, pages: int, page_size: int) -> Tuple[int, ...]:
+        return (pages, self.num_kv_heads, page_size, self.head_dim)
+
+    def elements_per_token(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+
+@dataclass(frozen=True)
 class StateNeed(PerRequestNeed):
     """A tensor of fixed ``shape`` per request, carried from step to step."""
 

@@ -49,6 +49,7 @@ struct DecodeTmaArgs {
   int nq, nkv, P, table_width, window;
   int n_rows, splits, split_keys;
   float scale;
+  int v_plane = 1;           // which plane of the cache holds the values (0: the keys are the values)
 };
 
 constexpr int DT_TILE = 64;
@@ -123,7 +124,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
 #pragma unroll
         for (int h = 0; h < NB; ++h) {
           tma_load_5d(st + h * KB, &tm_kv, h * 64, off, kvh, page, 0, &full_bar[s]);
-          tma_load_5d(st + (NB + h) * KB, &tm_kv, h * 64, off, kvh, page, 1, &full_bar[s]);
+          tma_load_5d(st + (NB + h) * KB, &tm_kv, h * 64, off, kvh, page, a.v_plane, &full_bar[s]);
         }
       }
       if (gave_up) {
@@ -399,7 +400,8 @@ extern "C" int ft_attn_decode_tma(const void* map_kv, const void* q, void* out, 
                                   float* part_ml, const int* rows, const int* token_pos,
                                   const int* token_seg, const int* block_table, int* status, int nq,
                                   int nkv, int d, int P, int table_width, int window, int n_rows,
-                                  int splits, int split_keys, float scale, cudaStream_t stream) {
+                                  int splits, int split_keys, float scale, int v_plane,
+                                  cudaStream_t stream) {
   if (n_rows <= 0) return FT_OK;
   if (nkv <= 0 || nq % nkv || splits < 1 || split_keys < DT_TILE || split_keys % DT_TILE || P % DT_TILE)
     return FT_ERR_SHAPE;
@@ -408,7 +410,7 @@ extern "C" int ft_attn_decode_tma(const void* map_kv, const void* q, void* out, 
   memcpy(&mkv, map_kv, sizeof(mkv));
   DecodeTmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, part_o, part_ml, rows, token_pos,
                   token_seg, block_table, status, nq, nkv, P, table_width, window, n_rows, splits,
-                  split_keys, scale};
+                  split_keys, scale, v_plane ? 1 : 0};
   int rc;
   switch (d) {
     case 64: rc = launch_decode_tma<64>(mkv, a, stream); break;

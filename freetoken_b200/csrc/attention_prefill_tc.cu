@@ -52,6 +52,7 @@ struct PrefillTcArgs {
   int* status;
   int nq, nkv, P, table_width;
   float scale_log2;          // sm_scale * log2(e)
+  int v_plane = 1;           // which plane of the cache holds the values (0: the keys are the values)
 };
 
 // HPC: query heads per CTA.  1: the CTA's 128 rows are 128 tokens of one head.
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
           mbar_expect_tx(&v_full[s], K_BYTES);
 #pragma unroll
           for (int h = 0; h < NB; ++h)
-            tma_load_5d(sVr + s * K_BYTES + h * KB, &tm_kv, h * 64, off, kvh, page, 1, &v_full[s]);
+            tma_load_5d(sVr + s * K_BYTES + h * KB, &tm_kv, h * 64, off, kvh, page, a.v_plane, &v_full[s]);
           ++v_issued;
         }
       }
@@ -467,9 +468,11 @@ int ft_attn_tc_kv_map(void* out, const void* base, long long pages, long long nk
   if ((d & 63) || P < AK || (head_stride & 7) || (page_stride & 7) || (kv_stride & 7) || ((uintptr_t)base & 15))
     return FT_ERR_SHAPE;
   CUtensorMap map;
-  cuuint64_t dims[5] = {(cuuint64_t)d, (cuuint64_t)P, (cuuint64_t)nkv, (cuuint64_t)pages, 2};
+  // kv_stride 0: a cache of one plane, read as keys and as values
+  cuuint64_t dims[5] = {(cuuint64_t)d, (cuuint64_t)P, (cuuint64_t)nkv, (cuuint64_t)pages,
+                        (cuuint64_t)(kv_stride ? 2 : 1)};
   cuuint64_t strides[4] = {(cuuint64_t)d * 2, (cuuint64_t)head_stride * 2, (cuuint64_t)page_stride * 2,
-                           (cuuint64_t)kv_stride * 2};
+                           (cuuint64_t)(kv_stride ? kv_stride : page_stride * pages) * 2};
   cuuint32_t box[5] = {64, AK, 1, 1, 1};
   cuuint32_t es[5] = {1, 1, 1, 1, 1};
   CUresult rc = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, (void*)base, dims, strides, box, es,
@@ -488,7 +491,7 @@ int ft_attn_tc_kv_map(void* out, const void* base, long long pages, long long nk
 int ft_attn_prefill_tc(const void* map_q, const void* map_q2, const void* map_kv, void* out, const int* tile_seg,
                        const int* tile_q0, const int* seg_q_start, const int* seg_pos0,
                        const int* block_table, int* status, int nq, int nkv, int d, int P,
-                       int table_width, int tiles, float scale, cudaStream_t stream) {
+                       int table_width, int tiles, float scale, int v_plane, cudaStream_t stream) {
   if (tiles <= 0) return FT_OK;
   if (nkv <= 0 || nq % nkv || P % AK) return FT_ERR_SHAPE;
   CUtensorMap mq, mq2, mkv;
@@ -497,7 +500,7 @@ int ft_attn_prefill_tc(const void* map_q, const void* map_q2, const void* map_kv
   memcpy(&mkv, map_kv, sizeof(mkv));
   const bool pair = ((nq / nkv) % 2) == 0;
   PrefillTcArgs a{(__nv_bfloat16*)out, tile_seg, tile_q0, seg_q_start, seg_pos0, block_table, status,
-                  nq, nkv, P, table_width, scale * 1.4426950408889634f};
+                  nq, nkv, P, table_width, scale * 1.4426950408889634f, v_plane ? 1 : 0};
   int rc;
   switch (d) {
     case 64:

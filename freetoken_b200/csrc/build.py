@@ -36,6 +36,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xc
 # library name -> source file; headers every library depends on
 LIBRARIES: Dict[str, str] = {
     "elementwise": "elementwise.cu",
+    "rowwise": "rowwise.cu",
     "gemm_simt": "gemm_simt.cu",
     "attention_simt": "attention_simt.cu",
     "moe_route": "moe_route.cu",

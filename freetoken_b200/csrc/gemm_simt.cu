@@ -30,6 +30,10 @@ struct GemmArgs {
   int M, N, K, G;
   int act;  // 0 silu(g)*u, 1 swigluoai
   float act_alpha, act_limit;
+  // batched use (one product per head of a mixer): blockIdx.z picks the batch, whose
+  // A, W and C start this many elements further on
+  long long a_batch_stride = 0, w_batch_stride = 0, c_batch_stride = 0;
+  int batch = 1;
 };
 
 __device__ __forceinline__ float glu_act(float g, float u, int act, float alpha, float limit) {
@@ -77,8 +81,8 @@ __global__ void __launch_bounds__(256) gemm_rows_kernel(GemmArgs a) {
   const int group = tile_info[0], row0 = tile_info[1], rows = tile_info[2];
   if (rows <= 0) return;
   const int n0 = blockIdx.y * BN;
-  const AT* A = (const AT*)a.A;
-  const WT* W = (const WT*)a.W + (size_t)group * a.w_group_stride;
+  const AT* A = (const AT*)a.A + (size_t)blockIdx.z * a.a_batch_stride;
+  const WT* W = (const WT*)a.W + (size_t)group * a.w_group_stride + (size_t)blockIdx.z * a.w_batch_stride;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
 
   float acc[TM][TN], acu[GLU ? TM : 1][GLU ? TN : 1];
@@ -132,7 +136,7 @@ __global__ void __launch_bounds__(256) gemm_rows_kernel(GemmArgs a) {
     __syncthreads();
   }
 
-  OT* C = (OT*)a.C;
+  OT* C = (OT*)a.C + (size_t)blockIdx.z * a.c_batch_stride;
 #pragma unroll
   for (int i = 0; i < TM; ++i) {
     const int r = ty + 16 * i;
@@ -177,8 +181,8 @@ __global__ void __launch_bounds__(256) gemm_dense_kernel(GemmArgs a) {
   __shared__ __align__(16) float As[TBK][TBM + 4];
   __shared__ __align__(16) float Ws[TBK][TBN + 4];
   const int row0 = blockIdx.x * TBM, n0 = blockIdx.y * TBN;
-  const AT* A = (const AT*)a.A;
-  const WT* W = (const WT*)a.W;
+  const AT* A = (const AT*)a.A + (size_t)blockIdx.z * a.a_batch_stride;
+  const WT* W = (const WT*)a.W + (size_t)blockIdx.z * a.w_batch_stride;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 8;      // this thread loads row lr, k lk..lk+7
   const bool a_ok = row0 + lr < a.M, w_ok = n0 + lr < a.N;
@@ -217,7 +221,7 @@ __global__ void __launch_bounds__(256) gemm_dense_kernel(GemmArgs a) {
     }
     __syncthreads();
   }
-  OT* C = (OT*)a.C;
+  OT* C = (OT*)a.C + (size_t)blockIdx.z * a.c_batch_stride;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int r = row0 + ty * 4 + i;
@@ -235,8 +239,9 @@ int launch(const GemmArgs& a, int glu, int max_tiles_hint, cudaStream_t stream) 
   const bool plain = !glu && !a.group_offsets && !a.a_rows && !a.c_rows && !a.row_scale;
   const int a_align = sizeof(AT) == 2 ? 7 : 3, w_align = sizeof(WT) == 2 ? 7 : 3;
   if (plain && a.M >= 64 && !(a.K & 31) && !(a.lda & a_align) && !(a.K & w_align) &&
+      !(a.a_batch_stride & a_align) && !(a.w_batch_stride & w_align) &&
       !((uintptr_t)a.A & 15) && !((uintptr_t)a.W & 15)) {
-    dim3 grid((a.M + 63) / 64, (a.N + 63) / 64);
+    dim3 grid((a.M + 63) / 64, (a.N + 63) / 64, a.batch);
     gemm_dense_kernel<AT, WT, OT><<<grid, 256, 0, stream>>>(a);
     return FT_OK;
   }
@@ -244,7 +249,7 @@ int launch(const GemmArgs& a, int glu, int max_tiles_hint, cudaStream_t stream) 
   const bool big = per_group >= 32;
   const int bm = big ? 64 : 16;
   const int tiles = (a.M + bm - 1) / bm + (a.group_offsets ? a.G : 0);
-  dim3 grid(tiles, (a.N + BN - 1) / BN);
+  dim3 grid(tiles, (a.N + BN - 1) / BN, a.batch);
   (void)max_tiles_hint;
   if (big) {
     if (glu) gemm_rows_kernel<AT, WT, OT, 64, true><<<grid, 256, 0, stream>>>(a);
@@ -259,6 +264,12 @@ int launch(const GemmArgs& a, int glu, int max_tiles_hint, cudaStream_t stream) 
 }  // namespace ft
 
 using namespace ft;
+
+// One dense product per batch entry (a head of a mixer): entry z reads A + z * a_batch_stride
+// ([M, K], row stride lda), W + z * w_batch_stride ([N, K]) and writes C + z * c_batch_stride.
+extern "C" int ft_gemm_heads(const void* A, int a_dtype, long long lda, long long a_batch_stride, const void* W,
+                             int w_dtype, long long w_batch_stride, void* C, int c_dtype, long long ldc,
+                             long long c_batch_stride, int M, int N, int K, int batch, cudaStream_t stream);
 
 // A, W, C element types are given by code; supported triples:
 //   (f32,f32,f32) (f32,bf16,f32) (bf16,bf16,bf16) (bf16,bf16,f32) (bf16,f32,f32)
@@ -279,6 +290,31 @@ extern "C" int ft_gemm_rows(const void* A, int a_dtype, long long lda, const voi
     case 111: rc = launch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(a, glu, 0, stream); break;
     case 110: rc = launch<__nv_bfloat16, __nv_bfloat16, float>(a, glu, 0, stream); break;
     case 100: rc = launch<__nv_bfloat16, float, float>(a, glu, 0, stream); break;
+    default: return FT_ERR_DTYPE;
+  }
+  if (rc != FT_OK) return rc;
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+extern "C" int ft_gemm_heads(const void* A, int a_dtype, long long lda, long long a_batch_stride, const void* W,
+                             int w_dtype, long long w_batch_stride, void* C, int c_dtype, long long ldc,
+                             long long c_batch_stride, int M, int N, int K, int batch, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return FT_OK;
+  if (K <= 0 || batch > 65535) return FT_ERR_SHAPE;
+  GemmArgs a{A, W, C, nullptr, nullptr, nullptr, nullptr, lda, ldc, 0, M, N, K, 1, 0, 0.f, 0.f};
+  a.a_batch_stride = a_batch_stride;
+  a.w_batch_stride = w_batch_stride;
+  a.c_batch_stride = c_batch_stride;
+  a.batch = batch;
+  const int key = a_dtype * 100 + w_dtype * 10 + c_dtype;
+  int rc;
+  switch (key) {
+    case 0: rc = launch<float, float, float>(a, 0, 0, stream); break;
+    case 10: rc = launch<float, __nv_bfloat16, float>(a, 0, 0, stream); break;
+    case 111: rc = launch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(a, 0, 0, stream); break;
+    case 110: rc = launch<__nv_bfloat16, __nv_bfloat16, float>(a, 0, 0, stream); break;
+    case 100: rc = launch<__nv_bfloat16, float, float>(a, 0, 0, stream); break;
     default: return FT_ERR_DTYPE;
   }
   if (rc != FT_OK) return rc;

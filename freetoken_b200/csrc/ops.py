@@ -90,6 +90,15 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> No
         raise KernelError(f"{name} must be contiguous")
 
 
+def _need_pages(kv_pages: torch.Tensor, dtype) -> None:
+    """Pages are ``[2 (K, V), pages, kv_heads, page, head_dim]`` with every plane dense.  A
+    cache whose values ARE its keys is one plane seen twice (a stride of 0 between the two)."""
+    _need(kv_pages, "kv_pages", dtype, contiguous=False)
+    if kv_pages.dim() != 5 or kv_pages.shape[0] != 2 or not kv_pages[0].is_contiguous() \
+            or kv_pages.stride(0) not in (0, kv_pages[0].numel()):
+        raise KernelError("kv_pages must be [2, pages, kv_heads, page, head_dim], planes dense")
+
+
 # ------------------------------------------------------------------ rows
 def embed_gather(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor) -> None:
     """residual[t,:] = float(table[ids[t],:])"""
@@ -217,7 +226,110 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor, dst: torch.Tensor) -> Non
     _check(f(_ptr(src), _ptr(rows), _ptr(dst), code(src.dtype), n, H, _stream()), "gather_rows")
 
 
+# -------------------------------------------- rows of one-tensor caches, gates, caps
+def embed_norm(ids: torch.Tensor, table: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
+               eps: float) -> None:
+    """residual[t,:] = rms(table[ids[t],:]) * weight  (float32)."""
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    _need(weight, "weight", torch.float32)
+    _need(residual, "residual", torch.float32)
+    T, H = residual.shape
+    if table.shape[1] != H or ids.numel() != T or weight.numel() != H:
+        raise KernelError("embed_norm: shapes do not match")
+    f = _fn("rowwise", "ft_embed_norm", "p p i p p i i i f")
+    _check(f(_ptr(ids), _ptr(table), code(table.dtype), _ptr(weight), _ptr(residual), T, H, table.shape[0],
+             float(eps), _stream()), "embed_norm")
+
+
+def key_store(src: torch.Tensor, q_out: Optional[torch.Tensor], pages: Optional[torch.Tensor],
+              k_weight: Optional[torch.Tensor], token_pos: torch.Tensor, token_seg: torch.Tensor,
+              block_table: torch.Tensor, *, q_off: int, k_off: int, num_heads: int, q_dim: int,
+              num_kv_heads: int, k_dim: int, temp_coef: float = 0.0, temp_every: int = 1,
+              eps: float = 0.0) -> None:
+    """What a mixer with one cached tensor per token does between its projection and its
+    attention.  ``src`` rows hold queries at ``q_off`` and keys at ``k_off``.
+
+    * ``q_out`` (``[T, heads * q_dim]``, or ``None``): the queries times the temperature
+      ``1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)`` of their position.
+    * ``pages`` (``[pages, kv_heads, page, k_dim]``, or ``None`` for a stop that reads another
+      stop's cache): the key rows, RMS-normed per key head and multiplied by ``k_weight`` when
+      that is given, stored at the token's place."""
+    _need(src, "src", contiguous=False)
+    T = src.shape[0]
+    if src.stride(1) != 1 or max(q_off + num_heads * q_dim if q_out is not None else 0,
+                                 k_off + num_kv_heads * k_dim) > src.shape[1]:
+        raise KernelError("key_store: src rows do not hold the queries and keys named")
+    for name, t in (("token_pos", token_pos), ("token_seg", token_seg), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if q_out is not None:
+        _need(q_out, "q_out", src.dtype)
+        if q_out.shape != (T, num_heads * q_dim):
+            raise KernelError("key_store: q_out must be [T, heads * q_dim]")
+    P, page_stride = 1, 0
+    if pages is not None:
+        _need(pages, "pages", src.dtype)
+        if pages.dim() != 4 or pages.shape[1] != num_kv_heads or pages.shape[3] != k_dim:
+            raise KernelError("key_store: pages must be [pages, kv_heads, page, k_dim]")
+        P, page_stride = pages.shape[2], pages.stride(0)
+    if k_weight is not None:
+        _need(k_weight, "k_weight", torch.float32)
+        if k_weight.numel() != k_dim:
+            raise KernelError("key_store: the norm weight has the wrong length")
+    f = _fn("rowwise", "ft_key_store", "p p p p p p p q q i i i i i i i i i f f i i")
+    _check(f(_ptr(src), _ptr(q_out), _ptr(pages), _ptr(k_weight), _ptr(token_pos), _ptr(token_seg),
+             _ptr(block_table), src.stride(0), page_stride, q_off, k_off, num_heads, q_dim, num_kv_heads,
+             k_dim, P, block_table.shape[1], int(temp_every), float(temp_coef), float(eps),
+             code(src.dtype), T, _stream()), "key_store")
+
+
+def gate_heads(o: torch.Tensor, z: torch.Tensor, heads: int, head_dim: int) -> None:
+    """o[t, h, :] *= sigmoid(z[t, h]); ``z`` may be a column range of a wider matrix."""
+    _need(o, "o")
+    _need(z, "z", o.dtype, contiguous=False)
+    T = o.shape[0]
+    if o.shape[1] != heads * head_dim or z.shape != (T, heads) or z.stride(1) != 1:
+        raise KernelError("gate_heads: shapes do not match")
+    f = _fn("rowwise", "ft_gate_heads", "p p q i i i i")
+    _check(f(_ptr(o), _ptr(z), z.stride(0), heads, head_dim, code(o.dtype), T, _stream()), "gate_heads")
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, kind: str) -> None:
+    """In place: ``relu2`` relu(x)^2, ``gelu_tanh``, ``silu``; float32 arithmetic."""
+    _need(x, "x")
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation: unknown kind {kind!r}")
+    f = _fn("rowwise", "ft_activation", "p q i i")
+    _check(f(_ptr(x), x.numel(), ACTIVATIONS[kind], code(x.dtype), _stream()), "activation")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """In place: x = cap * tanh(x / cap) (float32)."""
+    _need(x, "x", torch.float32)
+    f = _fn("rowwise", "ft_softcap", "p q f")
+    _check(f(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+
+
 # ------------------------------------------------------------------ gemm
+def gemm_heads(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> None:
+    """One product per head on CUDA cores in float32: ``c[:, h, :] = a[:, h, :] @ w[h]^T``
+    with ``a`` ``[T, heads, K]``, ``w`` ``[heads, N, K]`` (dense), ``c`` ``[T, heads, N]``;
+    ``a`` and ``c`` may be views with any row stride."""
+    _need(a, "a", contiguous=False)
+    _need(w, "w")
+    _need(c, "c", contiguous=False)
+    T, heads, K = a.shape
+    N = w.shape[1]
+    if w.shape != (heads, N, K) or c.shape != (T, heads, N) or a.stride(2) != 1 or c.stride(2) != 1:
+        raise KernelError("gemm_heads: shapes do not match")
+    f = _fn("gemm_simt", "ft_gemm_heads", "p i q q p i q p i q q i i i i")
+    _check(f(_ptr(a), code(a.dtype), a.stride(0), a.stride(1), _ptr(w), code(w.dtype), N * K, _ptr(c),
+             code(c.dtype), c.stride(0), c.stride(1), T, N, K, heads, _stream()), "gemm_heads")
+
+
 def gemm_rows(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
               group_offsets: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
               c_rows: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
@@ -474,7 +586,7 @@ def attn_paged_simt(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
     """Generic paged attention; ``rows`` limits it to those token rows."""
     _need(q, "q")
     _need(out, "out", q.dtype)
-    _need(kv_pages, "kv_pages", q.dtype)
+    _need_pages(kv_pages, q.dtype)
     for name, t in (("token_pos", token_pos), ("token_seg", token_seg), ("block_table", block_table)):
         _need(t, name, torch.int32)
     T = q.shape[0] if rows is None else rows.numel()
@@ -554,7 +666,7 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
     """Split-KV tensor-core attention for single-token rows (bfloat16)."""
     _need(q, "q", torch.bfloat16)
     _need(out, "out", torch.bfloat16)
-    _need(kv_pages, "kv_pages", torch.bfloat16)
+    _need_pages(kv_pages, torch.bfloat16)
     if not attn_decode_takes(q, head_dim):
         raise KernelError(f"attn_decode: head_dim {head_dim} not in {DECODE_HEAD_DIMS}")
     for name, t in (("token_pos", token_pos), ("token_seg", token_seg), ("block_table", block_table)):
@@ -581,11 +693,12 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
                       head_dim, kv_pages.stride(2), kv_pages.stride(1), kv_pages.stride(0))
         map_kv = _attn_tc_map("kv", (kv_pages.data_ptr(),) + tuple(kv_pages.shape) + tuple(kv_pages.stride()),
                               make_kv)
-        f = _fn("attention_decode_tma", "ft_attn_decode_tma", "p p p p p p p p p p i i i i i i i i i f")
+        f = _fn("attention_decode_tma", "ft_attn_decode_tma", "p p p p p p p p p p i i i i i i i i i f i")
         _check(f(ctypes.cast(map_kv, ctypes.c_void_p), _ptr(q), _ptr(out), _ptr(part_o), _ptr(part_ml),
                  _ptr(rows), _ptr(token_pos), _ptr(token_seg), _ptr(block_table), _ptr(tc_status(q.device)),
                  num_heads, num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1],
-                 int(window or 0), n_rows, splits, split_keys, float(scale), _stream()), "attn_decode_tma")
+                 int(window or 0), n_rows, splits, split_keys, float(scale),
+                 1 if kv_pages.stride(0) else 0, _stream()), "attn_decode_tma")
         if part_o is not None:
             fm = _fn("attention_decode", "ft_attn_merge", "p p p p i i i i")
             _check(fm(_ptr(part_o), _ptr(part_ml), _ptr(out), _ptr(rows), n_rows, num_heads, head_dim,
@@ -607,7 +720,7 @@ def attn_prefill(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
     ``tile_seg`` / ``tile_q0`` (bfloat16; head sizes of :data:`DECODE_HEAD_DIMS`)."""
     _need(q, "q", torch.bfloat16)
     _need(out, "out", torch.bfloat16)
-    _need(kv_pages, "kv_pages", torch.bfloat16)
+    _need_pages(kv_pages, torch.bfloat16)
     if not attn_decode_takes(q, head_dim):
         raise KernelError(f"attn_prefill: head_dim {head_dim} not in {DECODE_HEAD_DIMS}")
     for name, t in (("tile_seg", tile_seg), ("tile_q0", tile_q0), ("seg_q_start", seg_q_start),
@@ -687,12 +800,12 @@ def attn_prefill_tc(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
     map_kv = _attn_tc_map("kv", (kv_pages.data_ptr(),) + tuple(kv_pages.shape) + tuple(kv_pages.stride()),
                           make_kv)
     status = tc_status(q.device)
-    f = _fn("attention_prefill_tc", "ft_attn_prefill_tc", "p p p p p p p p p p i i i i i i f")
+    f = _fn("attention_prefill_tc", "ft_attn_prefill_tc", "p p p p p p p p p p i i i i i i f i")
     _check(f(ctypes.cast(map_q, ctypes.c_void_p), ctypes.cast(map_q2, ctypes.c_void_p),
              ctypes.cast(map_kv, ctypes.c_void_p), _ptr(out),
              _ptr(tile_seg), _ptr(tile_q0), _ptr(seg_q_start), _ptr(seg_pos0), _ptr(block_table),
              _ptr(status), num_heads, num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1],
-             tile_seg.numel(), float(scale), _stream()), "attn_prefill_tc")
+             tile_seg.numel(), float(scale), 1 if kv_pages.stride(0) else 0, _stream()), "attn_prefill_tc")
 
 
 # ---------------------------------------------------------------- router

@@ -33,8 +33,87 @@ PREFILL_TILE = 64
 _NORM_MODES = {"none": 0, "per_layer": 1, "per_head": 2}
 
 
+class PagedSoftmaxCore:
+    """What every mixer shares that runs causal softmax attention over paged keys and
+    values: the step metadata of the attention kernels and the choice among them.  A
+    mixer that mixes this in states ``nq`` (query heads), ``nkv`` (KV heads), ``d`` (head
+    size as the kernels see it), ``scale`` and ``window``."""
+
+    nq: int
+    nkv: int
+    d: int
+    scale: float
+    window = None
+
+    # ---- step metadata ---------------------------------------------------------
+    def step_plan_key(self):
+        # the lists depend on the step's segments only: every attention layer shares them
+        return "paged_attention"
+
+    def plan_step(self, shape: StepShape) -> StepPlan:
+        """What the attention kernels want to know about a step: which token rows
+        are single-token segments (decode kernel; listed only when the step also
+        has longer segments, otherwise it is all rows), the 64-token query tiles
+        of the longer segments (prefill kernels: segment and first token inside
+        it), how many query-key pairs those score, and the longest context of a
+        decode row (in whole block-table rows for a decode-only step, so that the
+        split count - and with it a captured graph - stays put while contexts grow)."""
+        segs = shape.segments
+        dec = [s.q_start for s in segs if s.n == 1]
+        tiles = [(i, q0) for i, s in enumerate(segs) if s.n > 1 for q0 in range(0, s.n, PREFILL_TILE)]
+        arrays = {
+            "tile_seg": np.asarray([t[0] for t in tiles], dtype=np.int32),
+            "tile_q0": np.asarray([t[1] for t in tiles], dtype=np.int32),
+        }
+        if dec and tiles:
+            arrays["decode_rows"] = np.asarray(dec, dtype=np.int32)
+        if shape.max_q_len == 1:
+            max_decode_kv = shape.table_width * shape.page_size
+        else:
+            max_decode_kv = max((s.pos0 + 1 for s in segs if s.n == 1), default=0)
+        host = {
+            "num_decode_rows": len(dec),
+            "num_prefill_tiles": len(tiles),
+            "prefill_scores": sum(s.n * (s.pos0 + (s.n + 1) // 2) for s in segs if s.n > 1),
+            "max_decode_kv_len": max_decode_kv,
+        }
+        return StepPlan(arrays=arrays, host=host)
+
+    def attention_libraries(self, dtype) -> List[str]:
+        fast = ["attention_decode", "attention_prefill"] if dtype == torch.bfloat16 else []
+        if fast and self.d in (64, 128):
+            # TMA-fed kernels (the prefill one also builds the tensor maps both use)
+            fast += ["attention_prefill_tc", "attention_decode_tma"]
+        return ["attention_simt"] + fast
+
+    def attend(self, ctx: StepContext, q, o, kv_pages, table) -> None:
+        """Single-token rows go to the split-KV tensor-core kernel, rows of
+        longer segments to a prefill kernel; sizes those refuse (and the
+        float32 path) go to the generic kernel.  ``kv_pages`` is ``[2 (K, V),
+        pages, kv_heads, page, head_dim]``."""
+        if ops.attn_decode_takes(q, self.d):
+            plan = ctx.plan(self)
+            n_dec, n_tiles = plan.host["num_decode_rows"], plan.host["num_prefill_tiles"]
+            if n_dec > 0:
+                ops.attn_decode(q, o, kv_pages, plan.tensors.get("decode_rows"), n_dec,
+                                ctx.token_pos, ctx.token_seg, table, self.nq, self.nkv, self.d,
+                                self.scale, self.window, plan.host["max_decode_kv_len"], ctx.workspace)
+            if n_tiles > 0:
+                tile_seg, tile_q0 = plan.tensors["tile_seg"], plan.tensors["tile_q0"]
+                if (plan.host["prefill_scores"] >= ops.PREFILL_TC_MIN_SCORES
+                        and ops.attn_prefill_tc_takes(q, kv_pages, self.d, self.window)):
+                    ops.attn_prefill_tc(q, o, kv_pages, tile_seg, tile_q0, ctx.seg_q_start,
+                                        ctx.seg_pos0, table, self.nq, self.nkv, self.d, self.scale)
+                    return
+                ops.attn_prefill(q, o, kv_pages, tile_seg, tile_q0, ctx.seg_q_start, ctx.seg_pos0,
+                                 table, self.nq, self.nkv, self.d, self.scale, self.window)
+            return
+        ops.attn_paged_simt(q, o, kv_pages, ctx.token_pos, ctx.token_seg, table,
+                            self.nq, self.nkv, self.d, self.scale, self.window)
+
+
 @register_mixer("paged_attention")
-class PagedAttention(Mixer):
+class PagedAttention(PagedSoftmaxCore, Mixer):
     """params: ``hidden_size, num_heads, num_kv_heads, head_dim, sm_scale,
     qk_norm`` (none | per_layer | per_head), ``qk_norm_eps, qk_norm_plus_one,
     sliding_window`` (None: all keys), ``position`` (a PartSpec), ``scope`` and
@@ -74,40 +153,6 @@ class PagedAttention(Mixer):
     def children(self):
         return [self.position]
 
-    # ---- step metadata ---------------------------------------------------------
-    def step_plan_key(self):
-        # the lists depend on the step's segments only: every attention layer shares them
-        return "paged_attention"
-
-    def plan_step(self, shape: StepShape) -> StepPlan:
-        """What the attention kernels want to know about a step: which token rows
-        are single-token segments (decode kernel; listed only when the step also
-        has longer segments, otherwise it is all rows), the 64-token query tiles
-        of the longer segments (prefill kernels: segment and first token inside
-        it), how many query-key pairs those score, and the longest context of a
-        decode row (in whole block-table rows for a decode-only step, so that the
-        split count - and with it a captured graph - stays put while contexts grow)."""
-        segs = shape.segments
-        dec = [s.q_start for s in segs if s.n == 1]
-        tiles = [(i, q0) for i, s in enumerate(segs) if s.n > 1 for q0 in range(0, s.n, PREFILL_TILE)]
-        arrays = {
-            "tile_seg": np.asarray([t[0] for t in tiles], dtype=np.int32),
-            "tile_q0": np.asarray([t[1] for t in tiles], dtype=np.int32),
-        }
-        if dec and tiles:
-            arrays["decode_rows"] = np.asarray(dec, dtype=np.int32)
-        if shape.max_q_len == 1:
-            max_decode_kv = shape.table_width * shape.page_size
-        else:
-            max_decode_kv = max((s.pos0 + 1 for s in segs if s.n == 1), default=0)
-        host = {
-            "num_decode_rows": len(dec),
-            "num_prefill_tiles": len(tiles),
-            "prefill_scores": sum(s.n * (s.pos0 + (s.n + 1) // 2) for s in segs if s.n > 1),
-            "max_decode_kv_len": max_decode_kv,
-        }
-        return StepPlan(arrays=arrays, host=host)
-
     # ---- cache and weights ------------------------------------------------
     def cache_need(self):
         return PagedKVNeed(self.nkv, self.d, self.window)
@@ -137,11 +182,7 @@ class PagedAttention(Mixer):
             self.w_knorm = tensors[self.n_knorm]
 
     def libraries(self, dtype) -> List[str]:
-        fast = ["attention_decode", "attention_prefill"] if dtype == torch.bfloat16 else []
-        if fast and self.d in (64, 128):
-            # TMA-fed kernels (the prefill one also builds the tensor maps both use)
-            fast += ["attention_prefill_tc", "attention_decode_tma"]
-        return ["elementwise", "attention_simt"] + fast + linear.libraries(dtype)
+        return ["elementwise"] + self.attention_libraries(dtype) + linear.libraries(dtype)
 
     # ---- forward ----------------------------------------------------------------
     def forward(self, ctx: StepContext, x: torch.Tensor, cache: CacheView) -> torch.Tensor:
@@ -158,29 +199,5 @@ class PagedAttention(Mixer):
             self.position.rotary_dim, self.norm_mode, self.norm_plus_one,
             self.position.interleaved, self.norm_eps)
         o = ws.get("attn.o", (T, qn), ctx.dtype)
-        self.attend(ctx, q, o, cache, table)
+        self.attend(ctx, q, o, cache.kv_pages, table)
         return linear.linear(o, self.w_o, ws.get("attn.y", (T, self.hidden), ctx.dtype))
-
-    def attend(self, ctx: StepContext, q, o, cache: CacheView, table) -> None:
-        """Single-token rows go to the split-KV tensor-core kernel, rows of
-        longer segments to a prefill kernel; sizes those refuse (and the
-        float32 path) go to the generic kernel."""
-        if ops.attn_decode_takes(q, self.d):
-            plan = ctx.plan(self)
-            n_dec, n_tiles = plan.host["num_decode_rows"], plan.host["num_prefill_tiles"]
-            if n_dec > 0:
-                ops.attn_decode(q, o, cache.kv_pages, plan.tensors.get("decode_rows"), n_dec,
-                                ctx.token_pos, ctx.token_seg, table, self.nq, self.nkv, self.d,
-                                self.scale, self.window, plan.host["max_decode_kv_len"], ctx.workspace)
-            if n_tiles > 0:
-                tile_seg, tile_q0 = plan.tensors["tile_seg"], plan.tensors["tile_q0"]
-                if (plan.host["prefill_scores"] >= ops.PREFILL_TC_MIN_SCORES
-                        and ops.attn_prefill_tc_takes(q, cache.kv_pages, self.d, self.window)):
-                    ops.attn_prefill_tc(q, o, cache.kv_pages, tile_seg, tile_q0, ctx.seg_q_start,
-                                        ctx.seg_pos0, table, self.nq, self.nkv, self.d, self.scale)
-                    return
-                ops.attn_prefill(q, o, cache.kv_pages, tile_seg, tile_q0, ctx.seg_q_start, ctx.seg_pos0,
-                                 table, self.nq, self.nkv, self.d, self.scale, self.window)
-            return
-        ops.attn_paged_simt(q, o, cache.kv_pages, ctx.token_pos, ctx.token_seg, table,
-                            self.nq, self.nkv, self.d, self.scale, self.window)

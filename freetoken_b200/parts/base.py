@@ -193,6 +193,10 @@ class Part:
     # (``ctx.segments``) other than through sizes that a graph key fixes - says
     # so; decode steps of a model are replayed from a graph only if all its parts do.
     graph_capturable = False
+    # A mixer or feed-forward whose ``forward`` takes ``out=`` (a ``[T, H]`` view whose rows
+    # may lie further apart than H) and leaves its result there says so; a block that wants
+    # the result in a place of its own copies it otherwise.
+    writes_into_out = False
 
     def __init__(self, spec: PartSpec, prefix: str):
         self.spec = spec

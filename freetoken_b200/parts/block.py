@@ -9,6 +9,16 @@ adds the pending branch output into the residual, then normalises::
     a = mixer(h)
     h = norm2(a, residual)          # residual += a
     return feed_forward(h)          # the next norm adds it
+
+``parallel`` has ONE norm whose output both sublayers read; the layer adds the
+sum of their outputs::
+
+    h = norm(delta, residual)       # residual += delta
+    return [mixer(h), feed_forward(h)]   # two partial rows per token
+
+The two outputs leave the block as ``[T, 2, H]``; the next norm adds them to each
+other and then to the residual in float32 (``x + (mixer + feed_forward)``).  A
+parallel layer may have no feed-forward; then it returns the mixer's rows alone.
 """
 
 from __future__ import annotations
@@ -26,3 +36,31 @@ class PreNormBlock(Block):
         a = self.mixer.forward(ctx, h, cache)
         h = self.feed_forward_norm.forward(ctx, a, residual)
         return self.feed_forward.forward(ctx, h)
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    NORM_NAMES = ("mixer",)
+    HAS_FEED_FORWARD = True          # or none: see check_parts
+
+    @classmethod
+    def check_parts(cls, prefix, norm_names, has_feed_forward) -> None:
+        if sorted(norm_names) != sorted(cls.NORM_NAMES):
+            raise ValueError(f"layer '{prefix}': a parallel block has the one norm {list(cls.NORM_NAMES)}, "
+                             f"the layer lists {sorted(norm_names)}")
+
+    def forward(self, ctx, delta, residual, cache):
+        h = self.mixer_norm.forward(ctx, delta, residual)
+        if self.feed_forward is None:
+            return self.mixer.forward(ctx, h, cache)
+        T, H = h.shape
+        pair = ctx.workspace.get("block.pair", (T, 2, H), ctx.dtype)
+        if self.mixer.writes_into_out:
+            self.mixer.forward(ctx, h, cache, out=pair[:, 0])
+        else:
+            pair[:, 0].copy_(self.mixer.forward(ctx, h, cache))
+        if self.feed_forward.writes_into_out:
+            self.feed_forward.forward(ctx, h, out=pair[:, 1])
+        else:
+            pair[:, 1].copy_(self.feed_forward.forward(ctx, h))
+        return pair

@@ -20,7 +20,8 @@ from .base import Norm, StepContext, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """params: ``size``, ``eps``, ``plus_one``, ``scope`` (tensor name below the prefix)."""
+    """params: ``size``, ``eps``, ``plus_one``, and ``scope`` (the tensor is ``<scope>.weight``
+    below the prefix) or ``tensor`` (its whole name below the prefix)."""
 
     graph_capturable = True
 
@@ -29,7 +30,7 @@ class RMSNorm(Norm):
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
         self.plus_one = bool(spec.get("plus_one", False))
-        self.weight_name = self.name(f"{spec.params['scope']}.weight")
+        self.weight_name = self.name(spec.get("tensor") or f"{spec.params['scope']}.weight")
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:

@@ -54,6 +54,8 @@ def known_architectures() -> Tuple[str, ...]:
 
 def architecture_of(config: Mapping[str, Any]) -> Architecture:
     names = config.get("architectures") or []
+    if not names and config.get("architecture"):
+        names = [config["architecture"]]          # some designs name themselves in the singular
     if not names:
         raise ValueError("config.json has no 'architectures' entry to choose the model by")
     return get_architecture(names[0])
@@ -88,4 +90,13 @@ def _load_builtin() -> None:
             rename_tensor=m3.rename_checkpoint_tensor,
         ),
         aliases=m3.ARCHITECTURES[1:],
+    )
+    from .config import fazinex
+    register_architecture(
+        Architecture(
+            name=fazinex.ARCHITECTURE,
+            read_config=fazinex.FazinexConfig.from_dict,
+            build_plan=fazinex.build_plan,
+            config_to_dict=lambda cfg: cfg.to_dict(),
+        ),
     )
