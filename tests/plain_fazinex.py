@@ -149,15 +149,15 @@ def random_state(config: dict, seed: int, std: float = 0.05) -> Dict[str, torch.
         st[p + "norm1"] = gain(W)
         H, d, dv = int(m["heads"]), int(m["dim"]), int(m["vdim"])
         s_in = 1.0 / math.sqrt(W)
-        st[p + "mix.q"] = mat(H * d, W, s=2.0 * s_in)
+        st[p + "mix.q"] = mat(H * d, W, s=s_in)
         if spec["type"] == "attention":
-            st[p + "mix.k"] = mat(int(m["kv_heads"]) * d, W, s=2.0 * s_in)
+            st[p + "mix.k"] = mat(int(m["kv_heads"]) * d, W, s=s_in)
             st[p + "mix.o"] = mat(W, H * d, s=1.0 / math.sqrt(H * d))
         else:
             R = int(m["kv_rank"])
             st[p + "mix.dkv"] = mat(R, W, s=s_in)
             st[p + "mix.dkv.norm"] = gain(R)
-            st[p + "mix.uk"] = mat(H * d, R, s=2.0 / math.sqrt(R))
+            st[p + "mix.uk"] = mat(H * d, R, s=1.0 / math.sqrt(R))
             st[p + "mix.uv"] = mat(H * dv, R, s=1.0 / math.sqrt(R))
             st[p + "mix.g"] = mat(H, W, s=2.0 * s_in)
             st[p + "mix.o"] = mat(W, H * dv, s=1.0 / math.sqrt(H * dv))
