@@ -120,11 +120,12 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
         const int j0 = k_begin + tile * TILE;
         const int page = table[j0 / a.P], off = j0 % a.P;
         unsigned char* st = stages + s * STAGE;
-        mbar_expect_tx(&full_bar[s], STAGE);
+        // a cache of one plane (v_plane 0): the key tile is the value tile too, fetched once
+        mbar_expect_tx(&full_bar[s], a.v_plane ? STAGE : STAGE / 2);
 #pragma unroll
         for (int h = 0; h < NB; ++h) {
           tma_load_5d(st + h * KB, &tm_kv, h * 64, off, kvh, page, 0, &full_bar[s]);
-          tma_load_5d(st + (NB + h) * KB, &tm_kv, h * 64, off, kvh, page, a.v_plane, &full_bar[s]);
+          if (a.v_plane) tma_load_5d(st + (NB + h) * KB, &tm_kv, h * 64, off, kvh, page, 1, &full_bar[s]);
         }
       }
       if (gave_up) {
@@ -172,7 +173,9 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) break;
     const unsigned char* tk = stages + stage * STAGE;
-    const unsigned char* tv = tk + NB * KB;
+    // one plane: the rows zeroed below are then key rows of this warp's own 16 keys, whose
+    // scores are masked by position
+    const unsigned char* tv = a.v_plane ? tk + NB * KB : tk;
     const int j0 = k_begin + tile * TILE + warp * 16;    // first key of this warp's 16
     if (j0 <= pos && j0 + 15 >= first_valid) {
       if (j0 + 15 > pos) {

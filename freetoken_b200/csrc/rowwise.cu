@@ -17,8 +17,22 @@
 namespace ft {
 
 // ------------------------------------------------------------- embed + norm
-template <typename WT>
-__global__ void __launch_bounds__(256)
+// 4 consecutive elements as float32
+__device__ __forceinline__ float4 load4f(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4f(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+constexpr int EMBED_THREADS = 256;
+constexpr int EMBED_KEEP = 4;      // groups of 4 elements a thread keeps between the two passes
+
+// VEC: rows of up to 4 * EMBED_THREADS * EMBED_KEEP elements, a multiple of 4, 16-byte aligned:
+// the row is read once and stays in registers between the sum of squares and the scaling.
+template <typename WT, bool VEC>
+__global__ void __launch_bounds__(EMBED_THREADS)
 embed_norm_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
                   const float* __restrict__ weight, float* __restrict__ residual, int H, int vocab,
                   float eps) {
@@ -30,13 +44,42 @@ embed_norm_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
   const WT* row = table + (size_t)id * H;
   float* out = residual + (size_t)t * H;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = to_float(row[i]);
-    ss += v * v;
+  if (VEC) {
+    float4 keep[EMBED_KEEP];
+    const int groups = H >> 2;
+#pragma unroll
+    for (int j = 0; j < EMBED_KEEP; ++j) {
+      const int gi = threadIdx.x + j * EMBED_THREADS;
+      if (gi < groups) {
+        const float4 v = load4f(row + 4 * gi);
+        keep[j] = v;
+        ss += v.x * v.x;
+        ss += v.y * v.y;
+        ss += v.z * v.z;
+        ss += v.w * v.w;
+      }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < EMBED_KEEP; ++j) {
+      const int gi = threadIdx.x + j * EMBED_THREADS;
+      if (gi < groups) {
+        const float4 w = load4f(weight + 4 * gi);
+        const float4 v = keep[j];
+        *reinterpret_cast<float4*>(out + 4 * gi) = make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z,
+                                                               v.w * inv * w.w);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float v = to_float(row[i]);
+      ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_float(row[i]) * inv * weight[i];
   }
-  ss = block_sum(ss, scratch);
-  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_float(row[i]) * inv * weight[i];
 }
 
 // ---------------------------------------------------------------- key store
@@ -53,28 +96,93 @@ struct KeyStoreArgs {
   float coef, eps;
 };
 
-template <typename AT>
-__global__ void __launch_bounds__(128) key_store_kernel(KeyStoreArgs a) {
+// 8 consecutive bfloat16 values as float32, and back
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  return raw;
+}
+
+// A block takes `tokens_per_block` tokens (1 when there are queries to scale: all its threads
+// share them; more when only keys are stored); a warp takes one (token, key head) row at a time.
+// VEC (bfloat16, everything a multiple of 8 elements and 16-byte aligned): 16-byte pieces.
+template <typename AT, bool VEC>
+__global__ void __launch_bounds__(128) key_store_kernel(KeyStoreArgs a, int T, int tokens_per_block) {
   pdl_wait();
-  const int t = blockIdx.x;
+  const int t0 = blockIdx.x * tokens_per_block;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const AT* row = (const AT*)a.src + (size_t)t * a.ld;
-  const int pos = a.token_pos[t];
   if (a.q_out) {
     // the temperature is a function of the position alone, in float32
+    const int t = t0;
+    const AT* q = (const AT*)a.src + (size_t)t * a.ld + a.q_off;
+    const int pos = a.token_pos[t];
     float temp = 1.f;
     if (a.coef != 0.f) temp = 1.f + a.coef * logf((float)((pos + 1) / a.every) + 1.f);
     AT* qo = (AT*)a.q_out + (size_t)t * a.nq * a.dq;
-    const AT* q = row + a.q_off;
-    for (int i = threadIdx.x; i < a.nq * a.dq; i += blockDim.x) qo[i] = from_float<AT>(to_float(q[i]) * temp);
+    const int n = a.nq * a.dq;
+    if (VEC) {
+      for (int c = threadIdx.x; c < (n >> 3); c += blockDim.x) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(q + 8 * c), v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= temp;
+        *reinterpret_cast<uint4*>(qo + 8 * c) = pack8(v);
+      }
+    } else {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) qo[i] = from_float<AT>(to_float(q[i]) * temp);
+    }
   }
   if (!a.pages) return;
-  const int page = a.block_table[(size_t)a.token_seg[t] * a.table_width + pos / a.P];
-  AT* dst = (AT*)a.pages + (size_t)page * a.page_stride + (size_t)(pos % a.P) * a.dk;
-  for (int g = warp; g < a.nkv; g += nwarps) {
-    const AT* k = row + a.k_off + (size_t)g * a.dk;
-    AT* kd = dst + (size_t)g * a.P * a.dk;
-    if (a.k_weight) {
+  for (int r = warp; r < tokens_per_block * a.nkv; r += nwarps) {
+    const int t = t0 + r / a.nkv, g = r % a.nkv;
+    if (t >= T) break;
+    const int pos = a.token_pos[t];
+    const int page = a.block_table[(size_t)a.token_seg[t] * a.table_width + pos / a.P];
+    const AT* k = (const AT*)a.src + (size_t)t * a.ld + a.k_off + (size_t)g * a.dk;
+    AT* kd = (AT*)a.pages + (size_t)page * a.page_stride + ((size_t)g * a.P + pos % a.P) * a.dk;
+    if (VEC) {
+      const int chunks = a.dk >> 3;
+      float first[8];                       // the lane's first piece stays in registers
+      float ss = 0.f;
+      for (int c = lane; c < chunks; c += 32) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(k + 8 * c), v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          ss += v[i] * v[i];
+          if (c == lane) first[i] = v[i];
+        }
+      }
+      float inv = 1.f;
+      if (a.k_weight) inv = 1.0f / sqrtf(warp_sum(ss) / (float)a.dk + a.eps);
+      for (int c = lane; c < chunks; c += 32) {
+        float v[8];
+        if (c == lane) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = first[i];
+        } else {
+          unpack8(*reinterpret_cast<const uint4*>(k + 8 * c), v);
+        }
+        if (a.k_weight) {
+          const float4 w0 = *reinterpret_cast<const float4*>(a.k_weight + 8 * c);
+          const float4 w1 = *reinterpret_cast<const float4*>(a.k_weight + 8 * c + 4);
+          v[0] *= inv * w0.x; v[1] *= inv * w0.y; v[2] *= inv * w0.z; v[3] *= inv * w0.w;
+          v[4] *= inv * w1.x; v[5] *= inv * w1.y; v[6] *= inv * w1.z; v[7] *= inv * w1.w;
+        }
+        *reinterpret_cast<uint4*>(kd + 8 * c) = pack8(v);
+      }
+    } else if (a.k_weight) {
       float ss = 0.f;
       for (int i = lane; i < a.dk; i += 32) {
         const float v = to_float(k[i]);
@@ -90,19 +198,32 @@ __global__ void __launch_bounds__(128) key_store_kernel(KeyStoreArgs a) {
 }
 
 // ------------------------------------------------------------------- gates
-// o[t, h, 0..d) *= sigmoid(z[t*ldz + h])
-template <typename AT>
+// o[t, h, 0..d) *= sigmoid(z[t*ldz + h]).  A thread owns PIECE consecutive elements of one head
+// (8 bfloat16 values as one 16-byte piece when d allows it), so the gate is evaluated once a piece.
+template <typename AT, int PIECE>
 __global__ void __launch_bounds__(256)
-gate_heads_kernel(AT* __restrict__ o, const AT* __restrict__ z, long long ldz, int heads, int d, long long n) {
+gate_heads_kernel(AT* __restrict__ o, const AT* __restrict__ z, long long ldz, int heads, int d, long long pieces) {
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  const long long th = i / d;
+  if (i >= pieces) return;
+  const long long th = i / (d / PIECE);
   const long long t = th / heads;
   const int h = (int)(th - t * heads);
   const float zz = to_float(z[t * ldz + h]);
   const float g = 1.f / (1.f + expf(-zz));
-  o[i] = from_float<AT>(to_float(o[i]) * g);
+  if (PIECE == 8) {
+    uint4* p = reinterpret_cast<uint4*>(o) + i;
+    uint4 raw = *p;
+    __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(v[j]);
+      v[j] = __floats2bfloat162_rn(f.x * g, f.y * g);
+    }
+    *p = raw;
+  } else {
+    o[i] = from_float<AT>(to_float(o[i]) * g);
+  }
 }
 
 // -------------------------------------------------------------- activation
@@ -152,9 +273,18 @@ extern "C" {
 int ft_embed_norm(const int* ids, const void* table, int table_dtype, const float* weight, float* residual,
                   int T, int H, int vocab, float eps, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
-  FT_DISPATCH(table_dtype, WT,
-              launch_pdl(embed_norm_kernel<WT>, dim3(T), dim3(256), 0, stream, ids, (const WT*)table, weight,
-                         residual, H, vocab, eps));
+  const bool vec = !(H & 3) && H <= 4 * EMBED_THREADS * EMBED_KEEP && !((uintptr_t)table & 15) &&
+                   !((uintptr_t)weight & 15) && !((uintptr_t)residual & 15) &&
+                   (table_dtype == FT_DTYPE_F32 || !(H & 7));
+  if (vec) {
+    FT_DISPATCH(table_dtype, WT,
+                (launch_pdl(embed_norm_kernel<WT, true>, dim3(T), dim3(EMBED_THREADS), 0, stream, ids,
+                            (const WT*)table, weight, residual, H, vocab, eps)));
+  } else {
+    FT_DISPATCH(table_dtype, WT,
+                (launch_pdl(embed_norm_kernel<WT, false>, dim3(T), dim3(EMBED_THREADS), 0, stream, ids,
+                            (const WT*)table, weight, residual, H, vocab, eps)));
+  }
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
@@ -167,7 +297,17 @@ int ft_key_store(const void* src, void* q_out, void* pages, const float* k_weigh
   if (nkv <= 0 || dk <= 0 || P <= 0 || (coef != 0.f && every <= 0)) return FT_ERR_SHAPE;
   KeyStoreArgs a{src, q_out, pages, k_weight, token_pos, token_seg, block_table, ld, page_stride,
                  q_off, k_off, nq, dq, nkv, dk, P, table_width, every, coef, eps};
-  FT_DISPATCH(dtype, AT, launch_pdl(key_store_kernel<AT>, dim3(T), dim3(128), 0, stream, a));
+  // with queries to scale a block takes one token; rows of keys alone are dealt out four tokens a block
+  const int per_block = q_out ? 1 : (nkv >= 4 ? 1 : 4 / nkv);
+  const dim3 grid((T + per_block - 1) / per_block);
+  const bool vec = dtype == FT_DTYPE_BF16 && !(ld & 7) && !(q_off & 7) && !(k_off & 7) && !(dk & 7) &&
+                   !((nq * dq) & 7) && !(page_stride & 7) && !((uintptr_t)src & 15) && !((uintptr_t)q_out & 15) &&
+                   !((uintptr_t)pages & 15) && !((uintptr_t)k_weight & 15);
+  if (vec) {
+    launch_pdl(key_store_kernel<__nv_bfloat16, true>, grid, dim3(128), 0, stream, a, T, per_block);
+  } else {
+    FT_DISPATCH(dtype, AT, (launch_pdl(key_store_kernel<AT, false>, grid, dim3(128), 0, stream, a, T, per_block)));
+  }
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
@@ -175,10 +315,17 @@ int ft_key_store(const void* src, void* q_out, void* pages, const float* k_weigh
 int ft_gate_heads(void* o, const void* z, long long ldz, int heads, int d, int dtype, int T, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   const long long n = (long long)T * heads * d;
+  if (dtype == FT_DTYPE_BF16 && !(d & 7) && !((uintptr_t)o & 15)) {
+    const long long pieces = n >> 3;
+    launch_pdl(gate_heads_kernel<__nv_bfloat16, 8>, dim3((unsigned)((pieces + 255) / 256)), dim3(256), 0, stream,
+               (__nv_bfloat16*)o, (const __nv_bfloat16*)z, ldz, heads, d, pieces);
+    FT_LAUNCH_CHECK();
+    return FT_OK;
+  }
   const unsigned blocks = (unsigned)((n + 255) / 256);
   FT_DISPATCH(dtype, AT,
-              launch_pdl(gate_heads_kernel<AT>, dim3(blocks), dim3(256), 0, stream, (AT*)o, (const AT*)z, ldz,
-                         heads, d, n));
+              (launch_pdl(gate_heads_kernel<AT, 1>, dim3(blocks), dim3(256), 0, stream, (AT*)o, (const AT*)z, ldz,
+                          heads, d, n)));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

@@ -9,7 +9,8 @@ repetitions so that no repetition finds it in L2.
 
 Kernels: ``expert_gemv`` (decode experts, weight-streaming mma.sync kernel),
 ``lm_head`` (the same kernel, dense, float32 result), ``moe_gemm_tc`` (prefill
-experts on tcgen05/TMEM with TMA, 64 rows per expert; ``_busy``: 512 rows per expert), ``attn_decode`` (64 rows x 2,048 keys; ``_32k``: 8 rows x 32,768 keys), ``attn_prefill`` (mma.sync), ``attn_prefill_tc`` (tcgen05/TMEM, TMA-fed; ``_8k``: a
+experts on tcgen05/TMEM with TMA, 64 rows per expert; ``_busy``: 512 rows per expert), ``attn_decode`` (64 rows x 2,048 keys; ``_32k``: 8 rows x 32,768 keys; ``_one_plane``: the same rows over a cache
+whose one plane is keys and values), ``key_store`` (queries times temperature and keys to pages, 8,192 tokens), ``attn_prefill`` (mma.sync), ``attn_prefill_tc`` (tcgen05/TMEM, TMA-fed; ``_8k``: a
 8,192-token prompt),
 ``router`` (float32 router logits + top-k for a decode batch); ``*_flashinfer``: the same
 attention shapes through FlashInfer's trtllm-gen kernels (the reference's backend on
@@ -129,6 +130,42 @@ def attn_decode(sets: int = 2, B: int = 64, ctx: int = 2048):
     def run(i):
         ops.attn_decode(q, out, kv[i % sets], None, B, pos, seg, table, NQ, NKV, D, D ** -0.5, None, ctx, ws)
     return run, B * ctx * 2 * NKV * D * 2, 4.0 * B * NQ * D * ctx, "hbm"
+
+
+def attn_decode_one_plane(sets: int = 2, B: int = 64, ctx: int = 2048):
+    """The same decode rows over a cache of ONE plane, read as keys and as values (mixers whose
+    values are their keys, or that attend over a latent): half the bytes of ``attn_decode``."""
+    P = 64
+    width = ctx // P
+    pages = B * width + 1
+    planes = [torch.randn(pages, NKV, P, D, device=DEV, dtype=torch.bfloat16) for _ in range(sets)]
+    kv = [t.unsqueeze(0).expand(2, *t.shape) for t in planes]
+    table = (torch.randperm(pages - 1)[: B * width] + 1).to(torch.int32).view(B, width).to(DEV)
+    q = torch.randn(B, NQ * D, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
+    seg = torch.arange(B, dtype=torch.int32, device=DEV)
+    ws = Workspace(DEV)
+
+    def run(i):
+        ops.attn_decode(q, out, kv[i % sets], None, B, pos, seg, table, NQ, NKV, D, D ** -0.5, None, ctx, ws)
+    return run, B * ctx * NKV * D * 2, 4.0 * B * NQ * D * ctx, "hbm"
+
+
+def key_store(sets: int = 4, T: int = 8192):
+    """A prompt portion's rows: queries times their temperature, keys into their pages."""
+    P = 64
+    src = [torch.randn(T, (NQ + NKV) * D, device=DEV, dtype=torch.bfloat16) for _ in range(sets)]
+    q_out = torch.empty(T, NQ * D, device=DEV, dtype=torch.bfloat16)
+    pages = torch.zeros(T // P + 1, NKV, P, D, device=DEV, dtype=torch.bfloat16)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    seg = torch.zeros(T, dtype=torch.int32, device=DEV)
+    table = torch.arange(1, T // P + 1, dtype=torch.int32, device=DEV).view(1, -1)
+
+    def run(i):
+        ops.key_store(src[i % sets], q_out, pages, None, pos, seg, table, q_off=0, k_off=NQ * D, num_heads=NQ,
+                      q_dim=D, num_kv_heads=NKV, k_dim=D, temp_coef=0.1, temp_every=512)
+    return run, 2 * T * (NQ + NKV) * D * 2, 0.0, "hbm"
 
 
 def attn_decode_32k():
@@ -255,7 +292,8 @@ def router(sets: int = 8):
 
 KERNELS: Dict[str, Callable[[], Tuple[Callable[[int], None], int, float, str]]] = {
     "expert_gemv": expert_gemv, "lm_head": lm_head, "moe_gemm_tc": moe_gemm_tc, "moe_gemm_tc_busy": moe_gemm_tc_busy,
-    "attn_decode": attn_decode, "attn_decode_32k": attn_decode_32k, "attn_prefill": attn_prefill, "attn_prefill_tc": attn_prefill_tc,
+    "attn_decode": attn_decode, "attn_decode_one_plane": attn_decode_one_plane, "key_store": key_store,
+    "attn_decode_32k": attn_decode_32k, "attn_prefill": attn_prefill, "attn_prefill_tc": attn_prefill_tc,
     "attn_prefill_8k": attn_prefill_8k, "attn_prefill_tc_8k": attn_prefill_tc_8k, "router": router,
     "peak_copy": peak_copy, "peak_read": peak_read, "peak_gemm": peak_gemm,
     "attn_decode_flashinfer": attn_decode_flashinfer, "attn_decode_32k_flashinfer": attn_decode_32k_flashinfer,

@@ -117,6 +117,11 @@ def test_gate_activation_softcap_kernels():
     want = (o.cpu().double().view(T, H, d) * torch.sigmoid(z[:, 4:].cpu().double())[:, :, None]).view(T, H * d)
     ops.gate_heads(o, z[:, 4:], H, d)
     assert torch.allclose(o.cpu().double(), want, atol=1e-6)
+    ob = torch.randn(T, H * 16, device="cuda").to(torch.bfloat16)        # 16-byte pieces of a head
+    zb = (torch.randn(T, 4 + H, device="cuda") * 3).to(torch.bfloat16)
+    want = (ob.float().cpu().double().view(T, H, 16) * torch.sigmoid(zb[:, 4:].float().cpu().double())[:, :, None])
+    ops.gate_heads(ob, zb[:, 4:], H, 16)
+    assert torch.allclose(ob.float().cpu().double(), want.view(T, H * 16), atol=1e-2, rtol=1e-2)
     x = torch.linspace(-6, 6, 203, device="cuda")
     for kind, f in (("relu2", lambda v: torch.relu(v) ** 2),
                     ("gelu_tanh", lambda v: 0.5 * v * (1 + torch.tanh(math.sqrt(2 / math.pi) * (v + 0.044715 * v ** 3)))),
