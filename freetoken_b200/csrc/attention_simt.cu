@@ -29,7 +29,8 @@ struct AttnArgs {
   float scale;
 };
 
-template <typename AT, bool EXACT>
+// MAXD: output dims per lane (head sizes up to 32 * MAXD)
+template <typename AT, bool EXACT, int MAXD>
 __global__ void __launch_bounds__(128) attn_paged_kernel(AttnArgs a) {
   extern __shared__ float qs[];  // [4 warps][d]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -49,7 +50,6 @@ __global__ void __launch_bounds__(128) attn_paged_kernel(AttnArgs a) {
   const AT* kbase = (const AT*)a.kv_pages + (size_t)kvh * a.P * d;
   const AT* vbase = kbase + a.kv_stride;
 
-  constexpr int MAXD = 8;  // output dims per lane: head sizes up to 256
   float acc[MAXD];
 #pragma unroll
   for (int c = 0; c < MAXD; ++c) acc[c] = 0.f;
@@ -106,14 +106,19 @@ extern "C" int ft_attn_paged_simt(const void* q, void* out, const void* kv_pages
                                   int table_width, int window, float scale, int dtype, int T,
                                   cudaStream_t stream) {
   if (T <= 0) return FT_OK;
-  if (d > 256 || d <= 0 || nkv <= 0 || nq % nkv) return FT_ERR_SHAPE;
+  if (d > 512 || d <= 0 || nkv <= 0 || nq % nkv) return FT_ERR_SHAPE;
   AttnArgs a{q, out, kv_pages, token_pos, token_seg, block_table, rows, page_stride, kv_stride,
              nq, nkv, d, P, table_width, window, scale};
   dim3 grid(T, (nq + 3) / 4);
   const size_t smem = 4 * (size_t)d * sizeof(float);
-  if (dtype == FT_DTYPE_F32) attn_paged_kernel<float, true><<<grid, 128, smem, stream>>>(a);
-  else if (dtype == FT_DTYPE_BF16) attn_paged_kernel<__nv_bfloat16, false><<<grid, 128, smem, stream>>>(a);
-  else return FT_ERR_DTYPE;
+  if (dtype != FT_DTYPE_F32 && dtype != FT_DTYPE_BF16) return FT_ERR_DTYPE;
+  if (d <= 256) {
+    if (dtype == FT_DTYPE_F32) attn_paged_kernel<float, true, 8><<<grid, 128, smem, stream>>>(a);
+    else attn_paged_kernel<__nv_bfloat16, false, 8><<<grid, 128, smem, stream>>>(a);
+  } else {                      // head sizes up to 512 (a latent that is wider than any head)
+    if (dtype == FT_DTYPE_F32) attn_paged_kernel<float, true, 16><<<grid, 128, smem, stream>>>(a);
+    else attn_paged_kernel<__nv_bfloat16, false, 16><<<grid, 128, smem, stream>>>(a);
+  }
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

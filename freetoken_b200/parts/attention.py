@@ -80,7 +80,9 @@ class PagedSoftmaxCore:
         return StepPlan(arrays=arrays, host=host)
 
     def attention_libraries(self, dtype) -> List[str]:
-        fast = ["attention_decode", "attention_prefill"] if dtype == torch.bfloat16 else []
+        fast = []
+        if dtype == torch.bfloat16 and self.d in ops.DECODE_HEAD_DIMS:
+            fast = ["attention_decode", "attention_prefill"]
         if fast and self.d in (64, 128):
             # TMA-fed kernels (the prefill one also builds the tensor maps both use)
             fast += ["attention_prefill_tc", "attention_decode_tma"]

@@ -70,8 +70,8 @@ class SharedKVAttention(PagedSoftmaxCore, Mixer):
         self.window = p.get("sliding_window")
         if self.nkv <= 0 or self.nq % self.nkv:
             raise ValueError(f"num_heads {self.nq} is not a multiple of num_kv_heads {self.nkv}")
-        if self.d > 256:
-            raise ValueError(f"head_dim {self.d} exceeds what the attention kernels take (256)")
+        if self.d > 512:
+            raise ValueError(f"head_dim {self.d} exceeds what the attention kernels take (512)")
         if self.temp_coef != 0.0 and self.temp_every <= 0:
             raise ValueError("q_temp_every must be positive")
         names = p["names"]
@@ -138,8 +138,8 @@ class LatentAttention(PagedSoftmaxCore, Mixer):
         self.eps = float(p["norm_eps"])
         self.gated = bool(p.get("output_gate", True))
         self.window = None
-        if self.rank > 256:
-            raise ValueError(f"latent rank {self.rank} exceeds what the attention kernels take (256)")
+        if self.rank > 512:
+            raise ValueError(f"latent rank {self.rank} exceeds what the attention kernels take (512)")
         names = p["names"]
         scope = self.name(p["scope"])
         self.n = {k: f"{scope}.{v}" for k, v in names.items()}

@@ -165,6 +165,7 @@ ALONE = {
     "attention": one_layer(fz.attn(6, 3, 8, 0.5, coef=0.9, every=2)),
     "attention_no_temperature_one_key_head": one_layer(fz.attn(4, 1, 12, 0.4)),
     "latent": one_layer(fz.latent(3, 8, 12, 20, 0.5)),
+    "latent_wider_than_any_head": one_layer(fz.latent(2, 8, 8, 320, 0.3)),
     "feed_forward_beside_a_mixer": one_layer(fz.attn(1, 1, 8, 0.1, ff=40), logit_softcap=5.0),
 }
 
