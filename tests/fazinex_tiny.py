@@ -45,7 +45,7 @@ FZ_A: Dict = {
 
 # head sizes 32, 64 and 128 with pages of 64: the tensor-core and TMA-fed kernels
 FZ_B: Dict = {
-    "architecture": "Fazinex", "vocab": 300, "width": 128, "norm": {"eps": 1e-6},
+    "architecture": "Fazinex", "vocab": 300, "width": 128, "norm": {"eps": 2e-6},
     "layers": [attn(4, 2, 64, 0.125, coef=0.4, every=16, ff=96),
                latent(4, 32, 32, 64, 0.18, ff=64),
                attn(8, 1, 32, 0.2, coef=0.1, every=3),

@@ -148,3 +148,23 @@ def test_plain_latent_attention_is_attention_over_the_latent():
         out.append((p @ c) @ w["uv"].view(H, dv, R)[i].T * torch.sigmoid(h @ w["g"][i])[:, None])
     got = torch.cat(out, dim=1) @ w["o"].T
     assert torch.allclose(got, want, atol=1e-12)
+
+
+def test_random_model_command_writes_the_designs_tensors(tmp_path):
+    """``ft random-model`` on a Fazinex config: the folder holds the design's own tensor names
+    (separate q / k / dkv / g, not the merged projections the engine keeps), the plain
+    implementation runs on it, and norm weights are 1."""
+    import json
+
+    from freetoken_b200 import cli
+    from plain_model import read_safetensors
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(fz.FZ_A))
+    out = tmp_path / "model"
+    assert cli.main(["random-model", "--config", str(cfg_path), "--out", str(out), "--seed", "3"]) == 0
+    state = read_safetensors(str(out / "model.safetensors"))
+    assert set(state) == set(plain.random_state(fz.FZ_A, 0))
+    assert json.loads((out / "config.json").read_text()) == fz.FZ_A
+    assert torch.all(state["l1.mix.dkv.norm"].float() == 1) and torch.all(state["embed.norm"].float() == 1)
+    logits = plain.forward(fz.FZ_A, state, [1, 2, 3, 4])
+    assert logits.shape == (4, 200) and torch.isfinite(logits).all()

@@ -57,7 +57,7 @@ def test_embed_norm_kernel(dtype):
     assert torch.allclose(out.cpu().double(), want, atol=1e-5, rtol=1e-5)
 
 
-@pytest.mark.parametrize("every,coef", [(1, 0.7), (4, 0.5), (64, 0.3), (5, 0.0)])
+@pytest.mark.parametrize("every,coef", [(1, 0.7), (4, 0.5), (48, 0.35), (5, 0.0)])
 def test_key_store_temperature_and_pages(every, coef):
     """Queries times the temperature of their position - every position around every multiple
     of the period - and keys into the page and row of their position, two requests whose
@@ -134,8 +134,8 @@ def test_gate_activation_softcap_kernels():
         assert torch.allclose(yb.float().cpu().double(), f(x.to(torch.bfloat16)[:200].float().cpu().double()),
                               atol=1e-2, rtol=1e-2), kind
     logits = torch.linspace(-80, 80, 101, device="cuda").view(1, -1).contiguous()
-    want = 15 * torch.tanh(logits.cpu().double() / 15)
-    ops.softcap(logits, 15.0)
+    want = 12 * torch.tanh(logits.cpu().double() / 12)
+    ops.softcap(logits, 12.0)
     assert torch.allclose(logits.cpu().double(), want, atol=1e-5)
 
 
@@ -344,3 +344,30 @@ def test_greedy_generation_through_the_scheduler(models, which, dtype):
     assert ties == 0 if dtype == "float32" else ties <= 3
     if dtype == "bfloat16":
         assert llm.engine.graph_replays > 0
+
+
+def test_generate_command_and_sampling(models, capsys):
+    """``ft generate`` on a Fazinex folder in float32: greedy tokens are the plain model's; with a
+    temperature, a request's tokens depend on its seed and not on what else runs beside it."""
+    import json
+
+    from freetoken_b200 import LLM, SamplingParams, cli
+    config = fz.FZ["C"]
+    state = plain.random_state(config, fz.SEEDS["C"])
+    prompt = fz.tokens(3, 9, config["vocab"])
+    rc = cli.main(["generate", "--model-path", models["C"], "--dtype", "float32", "--page-size", "12",
+                   "--num-tokens", "240", "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "6",
+                   "--ignore-eos"])
+    assert rc == 0
+    result = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    seq = list(prompt)
+    for token in result["token_ids"]:
+        assert token == int(plain.forward(config, state, seq)[-1].argmax())
+        seq.append(token)
+    llm = LLM(models["C"], "float32", page_size=12, num_token_override=480, max_running_req=3)
+    sp = SamplingParams(temperature=0.8, top_k=20, top_p=0.9, max_tokens=8, ignore_eos=True, seed=5)
+    alone = llm.generate([prompt], sp)[0]["token_ids"]
+    beside = llm.generate([fz.tokens(4, 30, config["vocab"]), prompt, fz.tokens(5, 2, config["vocab"])],
+                          [SamplingParams(temperature=1.0, max_tokens=8, ignore_eos=True, seed=1), sp,
+                           SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)])[1]["token_ids"]
+    assert alone == beside and len(alone) == 8
