@@ -93,6 +93,7 @@ class FazinexConfig:
             fields: Dict[str, Any] = dict(type=kind, heads=heads, dim=dim, vdim=int(m.get("vdim") or dim),
                                           scale=float(need(m, "scale", mw)))
             if kind == "attention":
+                fields["vdim"] = dim          # the values are the keys: they have the keys' size
                 fields["kv_heads"] = int(m.get("kv_heads") or heads)
                 temp = m.get("q_temp")
                 if temp:
@@ -148,9 +149,6 @@ class FazinexConfig:
                 if m.kv_heads <= 0 or m.heads % m.kv_heads:
                     raise ConfigError(f"config.json: '{where}.kv_heads' = {m.kv_heads} does not divide "
                                       f"heads = {m.heads}")
-                if m.vdim != m.dim:
-                    raise ConfigError(f"config.json: '{where}.vdim' = {m.vdim} differs from dim = {m.dim}, "
-                                      f"but the values of this mixer are its keys")
                 if m.q_temp_coef != 0.0 and m.q_temp_every <= 0:
                     raise ConfigError(f"config.json: '{where}.q_temp.every' must be positive")
             elif m.kv_rank <= 0:

@@ -379,9 +379,11 @@ def skinny_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
                 active: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
                 c_rows: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
                 rows: Optional[int] = None, glu: bool = False, act: str = "silu",
-                act_alpha: float = 1.702, act_limit: float = 7.0, rows_per_pass: int = 8) -> None:
+                act_alpha: float = 1.702, act_limit: float = 7.0, rows_per_pass: int = 8,
+                unary: Optional[str] = None) -> None:
     """c = a @ w^T for few rows, streaming bfloat16 weights once through
-    mma.sync; same conventions as :func:`gemm_rows`."""
+    mma.sync; same conventions as :func:`gemm_rows`.  ``unary`` (one of
+    :data:`ACTIVATIONS`, without ``glu``): that function of the float32 accumulator is stored."""
     _need(a, "a", torch.bfloat16, contiguous=False)
     _need(w, "w", torch.bfloat16)
     _need(c, "c", contiguous=False)
@@ -403,11 +405,13 @@ def skinny_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
         _need(active, "active", torch.int32)
         if active.numel() < G + 1:
             raise KernelError("skinny_gemm: the active list needs G + 1 entries")
-    f = _fn("skinny_gemm", "ft_skinny_gemm", "p q p q p i q p p p p p i i i i i i f f i")
+    if unary is not None and (glu or unary not in ACTIVATIONS):
+        raise KernelError(f"skinny_gemm: cannot apply {unary!r} (with glu: {glu})")
+    f = _fn("skinny_gemm", "ft_skinny_gemm", "p q p q p i q p p p p p i i i i i i f f i i")
     _check(f(_ptr(a), a.stride(0), _ptr(w), NW * K, _ptr(c), code(c.dtype), c.stride(0),
              _ptr(group_offsets), _ptr(active), _ptr(a_rows), _ptr(c_rows), _ptr(row_scale), M, N, K, G,
              int(glu), 0 if act == "silu" else 1, float(act_alpha), float(act_limit),
-             rows_per_pass, _stream()), "skinny_gemm")
+             rows_per_pass, 0 if unary is None else 1 + ACTIVATIONS[unary], _stream()), "skinny_gemm")
 
 
 # ------------------------------------------------ grouped GEMM on tcgen05

@@ -38,6 +38,7 @@ struct SkinnyArgs {
   int M, N, K, G;
   int act;
   float act_alpha, act_limit;
+  int unary = 0;             // without GLU: 0 nothing, 1 relu(x)^2, 2 tanh-GELU, 3 SiLU on the accumulator
 };
 
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
@@ -62,6 +63,15 @@ __device__ __forceinline__ float glu_act_s(float g, float u, int act, float alph
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
   return (g / (1.f + __expf(-alpha * g))) * (u + 1.f);
+}
+
+__device__ __forceinline__ float unary_act_s(float x, int kind) {
+  switch (kind) {
+    case 1: { const float r = fmaxf(x, 0.f); return r * r; }
+    case 2: return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    case 3: return x / (1.f + expf(-x));
+    default: return x;
+  }
 }
 
 // KS: warps per block, splitting K.  2 for the experts (gate_up bank: measured against 4
@@ -180,7 +190,7 @@ __global__ void __launch_bounds__(KS * 32) skinny_kernel(SkinnyArgs a) {
       const int row = pass + 8 * j + tok, n = n0 + r;
       if (row < row_end && n < a.N) {
         const int crow = a.c_rows ? a.c_rows[row] : row;
-        float v = GLU ? glu_act_s(s, su, a.act, a.act_alpha, a.act_limit) : s;
+        float v = GLU ? glu_act_s(s, su, a.act, a.act_alpha, a.act_limit) : (a.unary ? unary_act_s(s, a.unary) : s);
         if (a.row_scale) v *= a.row_scale[crow];
         C[(size_t)crow * a.ldc + n] = from_float<OT>(v);
       }
@@ -227,7 +237,7 @@ extern "C" int ft_skinny_gemm(const void* A, long long lda, const void* W,
                               long long w_group_stride, void* C, int c_dtype, long long ldc,
                               const int* group_offsets, const int* active, const int* a_rows,
                               const int* c_rows, const float* row_scale, int M, int N, int K, int G, int glu,
-                              int act, float act_alpha, float act_limit, int rows_per_pass,
+                              int act, float act_alpha, float act_limit, int rows_per_pass, int unary,
                               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return FT_OK;
   if (K <= 0 || (K & 7) || (lda & 7) || G <= 0) return FT_ERR_SHAPE;
@@ -235,6 +245,8 @@ extern "C" int ft_skinny_gemm(const void* A, long long lda, const void* W,
   if (G > 65535) return FT_ERR_SHAPE;
   SkinnyArgs a{(const __nv_bfloat16*)A, (const __nv_bfloat16*)W, C, group_offsets, active, a_rows,
                c_rows, row_scale, lda, ldc, w_group_stride, M, N, K, G, act, act_alpha, act_limit};
+  if (unary < 0 || unary > 3 || (glu && unary)) return FT_ERR_SHAPE;
+  a.unary = unary;
   // with the list of busy groups, no more groups than rows can have any
   dim3 grid((N + 15) / 16, active ? min(G, M) : G);
   const int nt = rows_per_pass / 8;

@@ -75,7 +75,10 @@ def _kernel_times(fn: Callable[[], None], steps: int = 3) -> Dict[str, float]:
         for _ in range(steps):
             fn()
         torch.cuda.synchronize()
-    rows = {e.key: e.device_time_total / steps for e in prof.key_averages() if e.device_time_total > 0}
+    rows: Dict[str, float] = {}
+    for e in prof.key_averages():
+        if e.device_time_total > 0:           # instantiations of one template are added up
+            rows[_short(e.key)] = rows.get(_short(e.key), 0.0) + e.device_time_total / steps
     return dict(sorted(rows.items(), key=lambda kv: -kv[1]))
 
 
@@ -114,7 +117,7 @@ def measure_model(config: Dict[str, Any], a, seed: int = 0) -> Dict[str, Any]:
     out["prefill"] = {"tokens": a.prefill_tokens, "ms": round(ms, 3),
                       "tokens_per_s": round(a.prefill_tokens / (ms / 1e3))}
     kernels = _kernel_times(prefill_once)
-    out["prefill"]["kernel_us"] = {_short(k): round(v, 1) for k, v in list(kernels.items())[:10]}
+    out["prefill"]["kernel_us"] = {k: round(v, 1) for k, v in list(kernels.items())[:10]}
     out["prefill"]["kernel_us_total"] = round(sum(kernels.values()), 1)
 
     ids = [f"d{i}" for i in range(batch)]
@@ -139,7 +142,7 @@ def measure_model(config: Dict[str, Any], a, seed: int = 0) -> Dict[str, Any]:
                                "graph_replays": engine.graph_replays}
         if b == batch:
             kernels = _kernel_times(decode_once)
-            out[f"decode_b{b}"]["kernel_us"] = {_short(k): round(v, 1) for k, v in list(kernels.items())[:10]}
+            out[f"decode_b{b}"]["kernel_us"] = {k: round(v, 1) for k, v in list(kernels.items())[:10]}
             out[f"decode_b{b}"]["kernel_us_total"] = round(sum(kernels.values()), 1)
     for r in ids:
         engine.end_request(r)

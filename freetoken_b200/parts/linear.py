@@ -16,14 +16,27 @@
 
 from __future__ import annotations
 
+from typing import Optional
 
 import torch
 
 from ..csrc import ops
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """``out = x @ weight^T``; ``weight`` is ``[N, K]``; ``out`` preallocated."""
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+           activation: Optional[str] = None) -> torch.Tensor:
+    """``out = f(x @ weight^T)``; ``weight`` is ``[N, K]``; ``out`` preallocated.  ``activation``
+    names ``f`` (one of ``ops.ACTIVATIONS``; ``None``: the product itself): the weight-streaming
+    kernel applies it to its float32 accumulator, behind the other products it is a launch
+    of its own on the stored result."""
+    if activation is not None:
+        if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_ROWS
+                and ops.skinny_gemm_takes(x, weight, out)):
+            ops.skinny_gemm(x, weight, out, rows_per_pass=ops.pass_rows(x.shape[0]), unary=activation)
+            return out
+        linear(x, weight, out)
+        ops.activation(out, activation)
+        return out
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
         rows = x.shape[0]
         takes = ops.skinny_gemm_takes(x, weight, out)

@@ -54,8 +54,8 @@ class DenseMLP(FeedForward):
     def forward(self, ctx: StepContext, x: torch.Tensor, out=None) -> torch.Tensor:
         T = x.shape[0]
         ws = ctx.workspace
-        mid = linear.linear(x, self.w_up, ws.get("mlp.mid", (T, self.inter), ctx.dtype))
-        ops.activation(mid, self.act)
+        # decode rows: the activation is the weight-streaming kernel's epilogue
+        mid = linear.linear(x, self.w_up, ws.get("mlp.mid", (T, self.inter), ctx.dtype), activation=self.act)
         if out is None:
             out = ws.get("mlp.y", (T, self.hidden), ctx.dtype)
         return linear.linear(mid, self.w_down, out)

@@ -73,7 +73,7 @@ def test_refusals():
             node[path[-1]] = value
         return cfg
     for path, value in ((("vocab",), None), (("norm",), None), (("layers", 0, "type"), "mamba"),
-                        (("layers", 0, "mixer", "kv_heads"), 3), (("layers", 0, "mixer", "vdim"), 8),
+                        (("layers", 0, "mixer", "kv_heads"), 3),
                         (("layers", 1, "mixer", "kv_rank"), None), (("layers", 0, "mlp", "kind"), "routed"),
                         (("layers", 0, "mixer", "scale"), None)):
         with pytest.raises(ConfigError):

@@ -139,6 +139,27 @@ def test_gate_activation_softcap_kernels():
     assert torch.allclose(logits.cpu().double(), want, atol=1e-5)
 
 
+@pytest.mark.parametrize("rows", [1, 8, 20])
+@pytest.mark.parametrize("kind", ["relu2", "gelu_tanh", "silu"])
+def test_activation_in_the_weight_streaming_product(rows, kind):
+    """Few rows (decode): the up projection's activation is the product's epilogue, applied to
+    the float32 accumulator; more rows take the library product and the activation kernel."""
+    from freetoken_b200.parts import linear
+    torch.manual_seed(6)
+    K, N = 64, 40
+    x = torch.randn(rows, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.3).to(torch.bfloat16)
+    f = {"relu2": lambda v: torch.relu(v) ** 2, "silu": lambda v: v * torch.sigmoid(v),
+         "gelu_tanh": lambda v: 0.5 * v * (1 + torch.tanh(math.sqrt(2 / math.pi) * (v + 0.044715 * v ** 3)))}[kind]
+    want = f(x.float().cpu().double() @ w.float().cpu().double().T)
+    for r in (rows, rows + 40):
+        xx = x.repeat(-(-r // rows), 1)[:r].contiguous()
+        out = torch.empty(r, N, device="cuda", dtype=torch.bfloat16)
+        linear.linear(xx, w, out, activation=kind)
+        ref = want.repeat(-(-r // rows), 1)[:r]
+        assert torch.allclose(out.float().cpu().double(), ref, atol=3e-2, rtol=2e-2), (kind, r)
+
+
 @pytest.mark.parametrize("T", [1, 5, 130])
 def test_gemm_heads(T):
     """One product per head, on views with row strides of their own (both tile shapes)."""
