@@ -392,3 +392,59 @@ def test_generate_command_and_sampling(models, capsys):
                           [SamplingParams(temperature=1.0, max_tokens=8, ignore_eos=True, seed=1), sp,
                            SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)])[1]["token_ids"]
     assert alone == beside and len(alone) == 8
+
+
+# ------------------------------------------- the mixer's window option (no Fazinex model sets it)
+@pytest.mark.parametrize("dtype", list(DTYPES))
+@pytest.mark.parametrize("dim,page,window", [(16, 8, 24), (64, 64, 70)])
+def test_shared_kv_attention_with_a_window(tmp_path, monkeypatch, dim, page, window, dtype):
+    """``shared_kv_attention`` takes ``sliding_window`` like the engine's other attention mixer;
+    a variant architecture registered here sets it.  Attention is made sharp: the asking token
+    finds its target just inside the window (``window - 1`` back) and must not find it just
+    outside (``window`` back), in a prompt portion and as a decoded token; pages the window has
+    passed are given back while the requests run (head size 16: the generic kernel; 64: the
+    TMA-fed ones)."""
+    import dataclasses
+
+    from freetoken_b200.config import fazinex as fzc
+    from freetoken_b200.config.model_plan import PartSpec
+    from freetoken_b200.registry import Architecture, register_architecture
+
+    def build(cfg):
+        plan = fzc.build_plan(cfg)
+        layers = tuple(dataclasses.replace(l, mixer=PartSpec(l.mixer.kind, {**l.mixer.params, "sliding_window": window}))
+                       for l in plan.layers)
+        return dataclasses.replace(plan, layers=layers)
+    register_architecture(Architecture(name="FazinexWindowedForTest", read_config=fzc.FazinexConfig.from_dict,
+                                       build_plan=build, config_to_dict=lambda c: c.to_dict()))
+
+    def windowed_softmax(scores):
+        T = scores.shape[-1]
+        seen = torch.ones(T, T, dtype=torch.bool).tril() & ~torch.ones(T, T, dtype=torch.bool).tril(-window)
+        return torch.softmax(scores.masked_fill(~seen, float("-inf")), dim=-1)
+    monkeypatch.setattr(plain, "causal_softmax", windowed_softmax)
+
+    config = one_layer(fz.attn(2, 1, dim, 0.25, coef=0.2, every=32), vocab=120, width=48)
+    state = plain.random_state(config, 41)
+    asker, target = 7, 11
+    sharpen(config, state, 0, asker, target, beta=8.0)
+    n = 200
+    reqs = {}
+    for name, back in (("inside", window - 1), ("outside", window), ("far_outside", 3 * window)):
+        toks = [t if t not in (asker, target) else 13 for t in fz.tokens(60 + back, n, 120)]
+        for at in (n - 40, n - 1):            # asked from a prompt portion and by the last decoded token
+            toks[at] = asker
+            toks[at - back] = target
+        reqs[name] = toks
+    want = {rid: plain.forward(config, state, t) for rid, t in reqs.items()}
+    blind = [t if t != target else 13 for t in reqs["inside"]]
+    assert float(fz.position_errors(plain.forward(config, state, blind)[-1:], want["inside"][-1:])) > 0.3
+    seen = [t if t != target else 13 for t in reqs["outside"]]
+    assert float(fz.position_errors(plain.forward(config, state, seen)[-1:], want["outside"][-1:])) < 1e-9
+    folder = fz.write_model(str(tmp_path / "m"), {**config, "architecture": "FazinexWindowedForTest"}, state)
+    tol = fz.TOL[dtype] * (1 if dtype == "float32" else 3)
+    for cut in ("whole", "decode_tail", "portions", "mixed"):
+        schedule = CUTS[cut](reqs)
+        engine = fz.make_engine(folder, dtype, page, rd.peak_tokens(schedule, page), poison=True)
+        fz.compare(rd.run_engine(engine, reqs, schedule), want, tol, f"window {window}, {cut} [{dtype}]")
+        assert engine.cache.free_pages() == engine.cache.total_pages()
