@@ -29,8 +29,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Dict, List, Mapping, Optional, Tuple
 
-from .minimax_m3 import ConfigError
-from .model_plan import LayerSpec, ModelPlan, PartSpec, RunEntry
+from .model_plan import ConfigError, LayerSpec, ModelPlan, PartSpec, RunEntry
 
 ARCHITECTURE = "Fazinex"
 MIXER_TYPES = ("attention", "latent_attention")

@@ -24,17 +24,13 @@ import os
 from dataclasses import asdict, dataclass, fields
 from typing import Any, Dict, Mapping, Tuple
 
-from .model_plan import LayerSpec, ModelPlan, PartSpec, sequential_schedule
+from .model_plan import ConfigError, LayerSpec, ModelPlan, PartSpec, sequential_schedule
 
 ARCHITECTURES: Tuple[str, ...] = (
     "MiniMaxM3ForCausalLM",
     "MiniMaxM3SparseForCausalLM",
     "MiniMaxM3SparseForConditionalGeneration",
 )
-
-
-class ConfigError(ValueError):
-    """A config.json key is missing, malformed or asks for an unsupported feature."""
 
 
 @dataclass(frozen=True)

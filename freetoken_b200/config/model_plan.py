@@ -18,6 +18,10 @@ from dataclasses import dataclass, field
 from typing import Any, Dict, List, Mapping, Optional, Tuple
 
 
+class ConfigError(ValueError):
+    """A config.json key is missing, malformed or asks for an unsupported feature."""
+
+
 @dataclass(frozen=True)
 class PartSpec:
     """One part to build: a registry ``kind`` and its constructor parameters."""

@@ -11,7 +11,7 @@ import fazinex_tiny as fz
 import plain_fazinex as plain
 from freetoken_b200.cache import CacheManager, PagedKeyNeed
 from freetoken_b200.config.fazinex import FazinexConfig, build_plan
-from freetoken_b200.config.minimax_m3 import ConfigError
+from freetoken_b200.config import ConfigError
 from freetoken_b200.models import Model
 from freetoken_b200.registry import architecture_of
 
