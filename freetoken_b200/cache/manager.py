@@ -116,7 +116,37 @@ class StateNeed(PerRequestNeed):
     kind: str = "state"
 
 
-CacheNeed = PerTokenNeed | PerRequestNeed
+@dataclass(frozen=True)
+class CompositeNeed:
+    """What a mixer made of several mixers asks for: the needs of its members in their order
+    (``None`` for a member that keeps nothing).  Every member is pooled, paged and given state
+    slots exactly as if it were the mixer of a stop of its own; the manager knows the member by
+    the key ``(stop, index)`` (``(stop, index, index)`` for a member of a member)."""
+
+    parts: Tuple[Optional["CacheNeed"], ...]
+    kind: str = "composite"
+
+
+CacheNeed = PerTokenNeed | PerRequestNeed | CompositeNeed
+
+
+def flatten_needs(needs: Sequence[Optional[CacheNeed]]) -> List[Tuple[Hashable, CacheNeed]]:
+    """``(key, need)`` of every simple need: a stop's own need under the stop's index, the
+    members of a composite under ``(stop, index, ...)``."""
+    out: List[Tuple[Hashable, CacheNeed]] = []
+
+    def walk(key, need) -> None:
+        if need is None:
+            return
+        if isinstance(need, CompositeNeed):
+            base = key if isinstance(key, tuple) else (key,)
+            for j, part in enumerate(need.parts):
+                walk(base + (j,), part)
+            return
+        out.append((key, need))
+    for stop, need in enumerate(needs):
+        walk(stop, need)
+    return out
 
 
 @dataclass
@@ -124,7 +154,7 @@ class PageGroup:
     """Stops with the same paged need: own pool, own block table."""
 
     need: PerTokenNeed
-    stops: List[int]
+    stops: List[Hashable]
     pool: PagePool
     block_table: np.ndarray  # int32 [max_slots, max_pages_per_request], 0 = sink page
     # first page index still held, per slot (pages below it were given back)
@@ -136,7 +166,7 @@ class PageGroup:
 @dataclass
 class StateGroup:
     need: PerRequestNeed
-    stops: List[int]
+    stops: List[Hashable]
 
 
 class NoFreeSlot(RuntimeError):
@@ -149,7 +179,8 @@ class CacheManager:
     def __init__(self, needs: Sequence[Optional[CacheNeed]], page_size: int,
                  num_pages: int | Sequence[int], max_slots: int, max_seq_len: int):
         """``needs[i]`` is the need of the i-th cache-owning stop of the
-        schedule (``None``: that stop keeps nothing).  ``num_pages`` is the
+        schedule (``None``: that stop keeps nothing; a :class:`CompositeNeed`: one
+        entry per member).  ``num_pages`` is the
         pool size of every paged group, or one size per group in order of
         first appearance."""
         if page_size <= 0:
@@ -160,13 +191,11 @@ class CacheManager:
         self.max_pages_per_request = -(-max_seq_len // page_size)
         self.paged_groups: List[PageGroup] = []
         self.state_groups: List[StateGroup] = []
-        # stop -> (group index, index of the stop inside the group)
-        self.paged_index: Dict[int, Tuple[int, int]] = {}
-        self.state_index: Dict[int, Tuple[int, int]] = {}
+        # stop (or member key of a composite need) -> (group index, index inside the group)
+        self.paged_index: Dict[Hashable, Tuple[int, int]] = {}
+        self.state_index: Dict[Hashable, Tuple[int, int]] = {}
         paged_needs: List[PerTokenNeed] = []
-        for stop, need in enumerate(needs):
-            if need is None:
-                continue
+        for stop, need in flatten_needs(needs):
             if isinstance(need, PerTokenNeed):
                 if need not in paged_needs:
                     paged_needs.append(need)

@@ -39,13 +39,13 @@ class CacheStorage:
                 (len(g.stops), manager.max_slots + 1) + tuple(g.need.shape),
                 dtype=_STATE_DTYPES[g.need.dtype], device=self.device))
 
-    def kv_of_stop(self, stop: int) -> torch.Tensor:
+    def kv_of_stop(self, stop) -> torch.Tensor:
         """The pages of one cache-owning stop in its need's layout (keys and
         values: ``[2, pages, kv_heads, page_size, head_dim]``)."""
         g, i = self.manager.paged_index[stop]
         return self.paged[g][i]
 
-    def state_of_stop(self, stop: int) -> torch.Tensor:
+    def state_of_stop(self, stop) -> torch.Tensor:
         """``[slots + 1, *shape]`` of one cache-owning stop."""
         g, i = self.manager.state_index[stop]
         return self.state[g][i]
@@ -75,9 +75,9 @@ class CacheStorage:
 def kv_bytes_per_token(manager_needs, kv_dtype: torch.dtype) -> int:
     """Bytes one token costs over all stops that keep something per token
     (sizing the pool from free memory, cf. python/freetoken/kvcache/mha_pool.py:85-94)."""
-    from .manager import PerTokenNeed
+    from .manager import PerTokenNeed, flatten_needs
     total = 0
-    for need in manager_needs:
+    for _, need in flatten_needs(manager_needs):
         if isinstance(need, PerTokenNeed):
             dtype = kv_dtype if need.storage_dtype is None else _STATE_DTYPES[need.storage_dtype]
             total += need.elements_per_token() * torch.empty((), dtype=dtype).element_size()

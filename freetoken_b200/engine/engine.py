@@ -25,7 +25,7 @@ from typing import Any, Dict, Hashable, List, Mapping, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, CompositeNeed
 from ..cache.storage import CacheStorage, kv_bytes_per_token
 from ..csrc import build, ops
 from ..models.model import Model
@@ -137,13 +137,7 @@ class Engine:
         self.cache_views: List[CacheView] = []
         for i, stop in enumerate(self.plan.schedule):
             owner = self.plan.cache_owner(i)
-            view = CacheView(writes=(owner == i))
-            if owner in self.cache.paged_index:
-                view.kv_pages = self.storage.kv_of_stop(owner)
-                view.block_table_index = self.cache.paged_index[owner][0]
-            if owner in self.cache.state_index:
-                view.state = self.storage.state_of_stop(owner)
-            self.cache_views.append(view)
+            self.cache_views.append(self._cache_view(owner, needs[owner], writes=(owner == i)))
         self._pinned: List[torch.Tensor] = []
         self._pinned_events: List[torch.cuda.Event] = []
         self._pinned_turn = 0
@@ -154,6 +148,21 @@ class Engine:
         self.graph_replays = 0
         self.steps = 0
         self.tokens_run = 0
+
+    def _cache_view(self, key, need, writes: bool) -> CacheView:
+        """What the mixer whose need is ``need`` sees of the cache; the members of a composite
+        need get a view each, under the keys the manager knows them by."""
+        view = CacheView(writes=writes)
+        if isinstance(need, CompositeNeed):
+            base = key if isinstance(key, tuple) else (key,)
+            view.members = [self._cache_view(base + (j,), part, writes) for j, part in enumerate(need.parts)]
+            return view
+        if key in self.cache.paged_index:
+            view.kv_pages = self.storage.kv_of_stop(key)
+            view.block_table_index = self.cache.paged_index[key][0]
+        if key in self.cache.state_index:
+            view.state = self.storage.state_of_stop(key)
+        return view
 
     # ---- construction -----------------------------------------------------
     @classmethod

@@ -178,6 +178,8 @@ class CacheView:
     block_table_index: int = 0                   # which entry of ctx.block_tables
     state: Optional[torch.Tensor] = None         # [slots + 1, *shape]
     writes: bool = True                          # False: reads another stop's cache
+    # a mixer made of several mixers: one view per member, in the order of its composite need
+    members: List["CacheView"] = field(default_factory=list)
 
     @property
     def pages(self) -> Optional[torch.Tensor]:
