@@ -47,6 +47,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_prefill": "attention_prefill.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
     "moe_gemm_tc": "moe_gemm_tc.cu",
+    "recurrent": "recurrent.cu",
 }
 HEADERS: List[str] = ["common.cuh", "mma_utils.cuh", "tcgen05.cuh", "status_codes.h", "sampling_static.h"]
 EXTRA_LINK: Dict[str, List[str]] = {}

@@ -313,6 +313,174 @@ def softcap(x: torch.Tensor, cap: float) -> None:
     _check(f(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
 
 
+
+# ------------------------------------- sandwich norms, sums of mixers, biases, gated rows
+def norm_add(branch: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+             plus_one: bool, mult: float, part_scale: Optional[torch.Tensor] = None,
+             next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+             next_plus_one: bool = False, next_out: Optional[torch.Tensor] = None) -> None:
+    """residual += mult * rms(z) * (weight [+1]) with z = sum_j part_scale[j] * branch[:, j, :]
+    (``branch`` is ``[T, H]`` or ``[T, k, H]``; float32 throughout).  With ``next_weight`` the new
+    residual rows are RMS-normed once more into ``next_out``."""
+    _need(branch, "branch")
+    _need(residual, "residual", torch.float32)
+    _need(weight, "weight", torch.float32)
+    T, H = residual.shape
+    k = branch.shape[1] if branch.dim() == 3 else 1
+    if branch.shape[0] != T or branch.shape[-1] != H or weight.numel() != H:
+        raise KernelError("norm_add: shapes do not match")
+    if part_scale is not None:
+        _need(part_scale, "part_scale", torch.float32)
+        if part_scale.numel() != k:
+            raise KernelError("norm_add: one scale per partial row")
+    if next_weight is not None:
+        _need(next_weight, "next_weight", torch.float32)
+        _need(next_out, "next_out", branch.dtype)
+        if next_out.shape != residual.shape or next_weight.numel() != H:
+            raise KernelError("norm_add: the second norm's shapes do not match")
+    f = _fn("rowwise", "ft_norm_add", "p i p p i f f p p i f p i i i")
+    _check(f(_ptr(branch), k, _ptr(part_scale), _ptr(weight), int(plus_one), float(eps), float(mult),
+             _ptr(residual), _ptr(next_weight), int(next_plus_one), float(next_eps), _ptr(next_out), T, H,
+             code(branch.dtype), _stream()), "norm_add")
+
+
+def scaled_sum(parts: torch.Tensor, scale: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = sum_j scale[j] * parts[t, j, :] (float32 sum, ascending j)."""
+    _need(parts, "parts")
+    _need(scale, "scale", torch.float32)
+    _need(out, "out", parts.dtype)
+    T, k, H = parts.shape
+    if out.shape != (T, H) or scale.numel() != k:
+        raise KernelError("scaled_sum: shapes do not match")
+    f = _fn("rowwise", "ft_scaled_sum", "p p p i i i i")
+    _check(f(_ptr(parts), _ptr(scale), _ptr(out), k, T, H, code(out.dtype), _stream()), "scaled_sum")
+
+
+def bias_add(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """x[t, :] += bias, in place (float32 sum); rows of ``x`` may lie further apart than their width."""
+    _need(x, "x", contiguous=False)
+    _need(bias, "bias", torch.float32)
+    if x.dim() != 2 or x.stride(1) != 1 or bias.numel() != x.shape[1]:
+        raise KernelError("bias_add: x must be [T, width] with unit stride and one bias per column")
+    f = _fn("rowwise", "ft_bias_add", "p q p i i i")
+    _check(f(_ptr(x), x.stride(0), _ptr(bias), x.shape[0], x.shape[1], code(x.dtype), _stream()), "bias_add")
+
+
+def glu_rows(gate_up: torch.Tensor, mid: torch.Tensor, kind: str) -> None:
+    """mid[t, i] = f(gate_up[t, i]) * gate_up[t, I + i] with ``f`` one of :data:`ACTIVATIONS`."""
+    _need(gate_up, "gate_up")
+    _need(mid, "mid", gate_up.dtype)
+    T, I = mid.shape
+    if gate_up.shape != (T, 2 * I) or kind not in ACTIVATIONS:
+        raise KernelError("glu_rows: gate_up must be [T, 2 * I] and the activation a known one")
+    f = _fn("rowwise", "ft_glu_rows", "p p i i i i")
+    _check(f(_ptr(gate_up), _ptr(mid), T, I, ACTIVATIONS[kind], code(mid.dtype), _stream()), "glu_rows")
+
+
+# ------------------------------------------------------- mixers with a carried state
+def conv_silu(x: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+              state: torch.Tensor, token_seg: torch.Tensor, seg_slot: torch.Tensor,
+              seg_q_start: torch.Tensor) -> None:
+    """A causal convolution over time per channel, then SiLU: ``out[t, c] = silu(bias[c] +
+    sum_j weight[c, j] * u[t - (taps - 1) + j, c])`` where ``u`` is the request's inputs so far.
+    ``x`` ``[T, C]`` (a column range of a wider matrix is fine), ``state`` ``[slots, >= (taps - 1) *
+    C]`` float32: a request's last ``taps - 1`` inputs, read first and then brought up to date."""
+    _need(x, "x", contiguous=False)
+    _need(out, "out", x.dtype, contiguous=False)
+    _need(weight, "weight", torch.float32)
+    _need(state, "state", torch.float32, contiguous=False)
+    T, C = x.shape
+    taps = weight.shape[1]
+    if out.shape != x.shape or weight.shape[0] != C or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("conv_silu: shapes do not match")
+    if state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < (taps - 1) * C:
+        raise KernelError("conv_silu: a state row must hold taps - 1 inputs of every channel")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    for name, t in (("token_seg", token_seg), ("seg_slot", seg_slot), ("seg_q_start", seg_q_start)):
+        _need(t, name, torch.int32)
+    global LAUNCHES
+    LAUNCHES += 1 if taps > 1 else 0
+    f = _fn("recurrent", "ft_conv_silu", "p q p q p p p q p p p i i i i i")
+    _check(f(_ptr(x), x.stride(0), _ptr(out), out.stride(0), _ptr(weight), _ptr(bias), _ptr(state),
+             state.stride(0), _ptr(token_seg), _ptr(seg_slot), _ptr(seg_q_start), C, taps, T,
+             seg_slot.numel(), code(x.dtype), _stream()), "conv_silu")
+
+
+def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+             d_skip: torch.Tensor, state: torch.Tensor, y: torch.Tensor, seg_slot: torch.Tensor,
+             seg_q_start: torch.Tensor, heads: int, head_dim: int, state_dim: int, groups: int) -> None:
+    """Per head: ``S <- exp(-exp(a_log) * step) * S + step * B x^T``, ``y = S^T C + d_skip * x`` with
+    ``step = softplus(dt + dt_bias)``; ``xbc`` rows are ``x | B | C``; ``state`` ``[slots, >= heads *
+    state_dim * head_dim]`` float32; ``y`` ``[T, heads * head_dim]`` float32."""
+    _need(xbc, "xbc", contiguous=False)
+    _need(dt, "dt", xbc.dtype, contiguous=False)
+    _need(state, "state", torch.float32, contiguous=False)
+    _need(y, "y", torch.float32)
+    for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
+        _need(t, name, torch.float32)
+        if t.numel() != heads:
+            raise KernelError(f"ssd_scan: {name} must have one entry per head")
+    T = xbc.shape[0]
+    if xbc.shape[1] != heads * head_dim + 2 * groups * state_dim or dt.shape != (T, heads) \
+            or y.shape != (T, heads * head_dim) or xbc.stride(1) != 1 or dt.stride(1) != 1:
+        raise KernelError("ssd_scan: shapes do not match")
+    if state.stride(1) != 1 or state.shape[1] < heads * state_dim * head_dim:
+        raise KernelError("ssd_scan: a state row must hold heads * state_dim * head_dim values")
+    f = _fn("recurrent", "ft_ssd_scan", "p q p q p p p p q p p p i i i i i i")
+    _check(f(_ptr(xbc), xbc.stride(0), _ptr(dt), dt.stride(0), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip),
+             _ptr(state), state.stride(0), _ptr(y), _ptr(seg_slot), _ptr(seg_q_start), heads, head_dim,
+             state_dim, groups, seg_slot.numel(), code(xbc.dtype), _stream()), "ssd_scan")
+
+
+def delta_scan(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, dt_bias: torch.Tensor,
+               a_log: torch.Tensor, state: torch.Tensor, o: torch.Tensor, seg_slot: torch.Tensor,
+               seg_q_start: torch.Tensor, heads: int, key_heads: int, key_dim: int, value_dim: int,
+               unit_eps: float, q_scale: float) -> None:
+    """The gated delta rule per head: q and k made unit vectors (q times ``q_scale``), ``g =
+    exp(-exp(a_log) * softplus(decay + dt_bias))``, ``b = sigmoid(beta)``; ``S <- g S``; ``u = b (v -
+    S^T k)``; ``S <- S + k u^T``; ``o = S^T q``.  ``qkv`` rows are ``q | k | v``; ``beta`` and ``decay``
+    ``[T, heads]`` with the same row stride; ``state`` ``[slots, >= heads * key_dim * value_dim]``."""
+    _need(qkv, "qkv", contiguous=False)
+    _need(beta, "beta", qkv.dtype, contiguous=False)
+    _need(decay, "decay", qkv.dtype, contiguous=False)
+    _need(state, "state", torch.float32, contiguous=False)
+    _need(o, "o", torch.float32)
+    for name, t in (("dt_bias", dt_bias), ("a_log", a_log)):
+        _need(t, name, torch.float32)
+        if t.numel() != heads:
+            raise KernelError(f"delta_scan: {name} must have one entry per head")
+    T = qkv.shape[0]
+    if qkv.shape[1] != 2 * key_heads * key_dim + heads * value_dim or beta.shape != (T, heads) \
+            or decay.shape != (T, heads) or o.shape != (T, heads * value_dim) or qkv.stride(1) != 1 \
+            or beta.stride(1) != 1 or decay.stride(1) != 1 or beta.stride(0) != decay.stride(0):
+        raise KernelError("delta_scan: shapes do not match")
+    if state.stride(1) != 1 or state.shape[1] < heads * key_dim * value_dim:
+        raise KernelError("delta_scan: a state row must hold heads * key_dim * value_dim values")
+    f = _fn("recurrent", "ft_delta_scan", "p q p p q p p p q p p p i i i i f f i i")
+    _check(f(_ptr(qkv), qkv.stride(0), _ptr(beta), _ptr(decay), beta.stride(0), _ptr(dt_bias), _ptr(a_log),
+             _ptr(state), state.stride(0), _ptr(o), _ptr(seg_slot), _ptr(seg_q_start), heads, value_dim,
+             key_dim, key_heads, float(unit_eps), float(q_scale), seg_slot.numel(), code(qkv.dtype),
+             _stream()), "delta_scan")
+
+
+def gated_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, groups: int,
+               eps: float, gate_first: bool) -> None:
+    """Rows of float32 ``y`` in ``groups`` equal parts, each divided by its own root mean square,
+    times ``weight`` (repeated along the row when shorter); ``silu(gate)`` multiplies the values
+    before the norm (``gate_first``) or the result."""
+    _need(y, "y", torch.float32)
+    _need(gate, "gate", out.dtype, contiguous=False)
+    _need(weight, "weight", torch.float32)
+    _need(out, "out")
+    T, width = y.shape
+    if gate.shape != y.shape or out.shape != y.shape or gate.stride(1) != 1 or width % groups \
+            or width % weight.numel():
+        raise KernelError("gated_norm: shapes do not match")
+    f = _fn("recurrent", "ft_gated_norm", "p p q p i p i i i f i i")
+    _check(f(_ptr(y), _ptr(gate), gate.stride(0), _ptr(weight), weight.numel(), _ptr(out), T, width, groups,
+             float(eps), int(gate_first), code(out.dtype), _stream()), "gated_norm")
+
 # ------------------------------------------------------------------ gemm
 def gemm_heads(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> None:
     """One product per head on CUDA cores in float32: ``c[:, h, :] = a[:, h, :] @ w[h]^T``

@@ -264,6 +264,92 @@ __global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ x, lon
   if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
 
+// ------------------------------------------------- a branch's own norm, then the residual
+// z = sum_j s_j * branch[t, j, :] (float32; s_j = 1 without scales); the residual takes
+// mult * rms(z) * (w [+1]).  With a second weight the new residual row is normed once more
+// in the same pass and leaves as the next sublayer's input.  A block owns a token; z, then the
+// new residual row, stay in shared memory between the passes.
+template <typename AT>
+__global__ void __launch_bounds__(256)
+norm_add_kernel(const AT* __restrict__ branch, int k, const float* __restrict__ part_scale,
+                const float* __restrict__ weight, int plus_one, float eps, float mult,
+                float* __restrict__ residual, const float* __restrict__ next_weight, int next_plus_one,
+                float next_eps, AT* __restrict__ next_out, int H) {
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  pdl_wait();
+  const int t = blockIdx.x;
+  const AT* b = branch + (size_t)t * k * H;
+  float* r = residual + (size_t)t * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float z = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const float v = to_float(b[(size_t)j * H + i]);
+      z = part_scale ? fmaf(part_scale[j], v, z) : z + v;
+    }
+    row[i] = z;
+    ss = fmaf(z, z, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  const float one = plus_one ? 1.f : 0.f;
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float x = r[i] + mult * (row[i] * inv * (weight[i] + one));
+    r[i] = x;
+    row[i] = x;
+    ss2 = fmaf(x, x, ss2);
+  }
+  if (!next_weight) return;
+  ss2 = block_sum(ss2, scratch);
+  const float inv2 = 1.0f / sqrtf(ss2 / (float)H + next_eps);
+  const float one2 = next_plus_one ? 1.f : 0.f;
+  AT* o = next_out + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<AT>(row[i] * inv2 * (next_weight[i] + one2));
+}
+
+// out[t, :] = sum_j s_j * parts[t, j, :]   (float32 sum, ascending j)
+template <typename AT>
+__global__ void __launch_bounds__(256)
+scaled_sum_kernel(const AT* __restrict__ parts, const float* __restrict__ scale, AT* __restrict__ out, int k,
+                  long long n, int H) {
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long t = i / H;
+  const int c = (int)(i - t * H);
+  float z = 0.f;
+  for (int j = 0; j < k; ++j) z = fmaf(scale[j], to_float(parts[((size_t)t * k + j) * H + c]), z);
+  out[i] = from_float<AT>(z);
+}
+
+// x[t, c] += bias[c]; rows may lie further apart than their width
+template <typename AT>
+__global__ void __launch_bounds__(256)
+bias_add_kernel(AT* __restrict__ x, long long ld, const float* __restrict__ bias, long long n, int width) {
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long t = i / width;
+  const int c = (int)(i - t * width);
+  AT* p = x + t * ld + c;
+  *p = from_float<AT>(to_float(*p) + bias[c]);
+}
+
+// mid[t, i] = f(gu[t, i]) * gu[t, I + i]: the gate and up halves of one merged projection
+template <typename AT>
+__global__ void __launch_bounds__(256)
+glu_rows_kernel(const AT* __restrict__ gu, AT* __restrict__ mid, long long n, int I, int kind) {
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long t = i / I;
+  const int c = (int)(i - t * I);
+  const AT* row = gu + (size_t)t * 2 * I;
+  mid[i] = from_float<AT>(act_apply(to_float(row[c]), kind) * to_float(row[I + c]));
+}
+
 }  // namespace ft
 
 using namespace ft;
@@ -351,6 +437,51 @@ int ft_softcap(float* x, long long n, float cap, cudaStream_t stream) {
   if (n <= 0) return FT_OK;
   if (!(cap > 0.f)) return FT_ERR_SHAPE;
   launch_pdl(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, cap);
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_norm_add(const void* branch, int k, const float* part_scale, const float* weight, int plus_one, float eps,
+                float mult, float* residual, const float* next_weight, int next_plus_one, float next_eps,
+                void* next_out, int T, int H, int dtype, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  if (k <= 0 || H <= 0 || H > 12288) return FT_ERR_SHAPE;
+  FT_DISPATCH(dtype, AT,
+              (launch_pdl(norm_add_kernel<AT>, dim3(T), dim3(256), (size_t)H * sizeof(float), stream,
+                          (const AT*)branch, k, part_scale, weight, plus_one, eps, mult, residual, next_weight,
+                          next_plus_one, next_eps, (AT*)next_out, H)));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_scaled_sum(const void* parts, const float* scale, void* out, int k, int T, int H, int dtype,
+                  cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  const long long n = (long long)T * H;
+  FT_DISPATCH(dtype, AT,
+              (launch_pdl(scaled_sum_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
+                          (const AT*)parts, scale, (AT*)out, k, n, H)));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_bias_add(void* x, long long ld, const float* bias, int T, int width, int dtype, cudaStream_t stream) {
+  if (T <= 0 || width <= 0) return FT_OK;
+  const long long n = (long long)T * width;
+  FT_DISPATCH(dtype, AT,
+              (launch_pdl(bias_add_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (AT*)x, ld,
+                          bias, n, width)));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_glu_rows(const void* gu, void* mid, int T, int I, int kind, int dtype, cudaStream_t stream) {
+  if (T <= 0 || I <= 0) return FT_OK;
+  if (kind < 0 || kind > 2) return FT_ERR_SHAPE;
+  const long long n = (long long)T * I;
+  FT_DISPATCH(dtype, AT,
+              (launch_pdl(glu_rows_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
+                          (const AT*)gu, (AT*)mid, n, I, kind)));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
