@@ -1,6 +1,6 @@
 """Parts a decoder layer is assembled from (see :mod:`.base` for the interfaces)."""
 
-from . import attention, block, embedding, key_attention, mlp, moe, norm, position  # noqa: F401  (registers the kinds)
+from . import attention, block, composite, embedding, key_attention, mlp, moe, norm, position, recurrent  # noqa: F401  (registers the kinds)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Block,
                    CacheView, Embedding, FeedForward, Head, Mixer, Norm, Part, Position, Segment,
                    StepContext, StepPlan, StepShape, Workspace, register_block, register_embedding,

@@ -120,9 +120,18 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
     qk_norm`` (none | per_layer | per_head), ``qk_norm_eps, qk_norm_plus_one,
     sliding_window`` (None: all keys), ``position`` (a PartSpec), ``scope`` and
     ``checkpoint_names`` (q, k, v, o, fused qkv, q_norm, k_norm tensor names
-    below the scope)."""
+    below the scope).
+
+    ``value_dim`` (default ``head_dim``): the size of a value head where it differs from the
+    size of a query / key head.  The kernels see heads of the larger size: the smaller
+    projection's matrix (and the output projection's columns) are filled up with zeros when
+    the weights are bound, which changes no score and no output and costs cache and
+    arithmetic only where the two sizes differ.  ``bias`` (default False): the q, k, v and o
+    projections add a bias (``checkpoint_names`` then also has q_bias, k_bias, v_bias, o_bias
+    and the fused qkv_bias)."""
 
     graph_capturable = True
+    writes_into_out = True
 
     def __init__(self, spec, prefix):
         super().__init__(spec, prefix)
@@ -130,7 +139,10 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
         self.hidden = int(p["hidden_size"])
         self.nq = int(p["num_heads"])
         self.nkv = int(p["num_kv_heads"])
-        self.d = int(p["head_dim"])
+        self.dk = int(p["head_dim"])
+        self.dv = int(p.get("value_dim") or self.dk)
+        self.d = max(self.dk, self.dv)          # the head size the kernels and the cache see
+        self.has_bias = bool(p.get("bias", False))
         self.scale = float(p["sm_scale"])
         self.norm_mode = _NORM_MODES[p.get("qk_norm", "none")]
         self.norm_eps = float(p.get("qk_norm_eps", 1e-6))
@@ -138,8 +150,10 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
         self.window = p.get("sliding_window")
         if self.nq % self.nkv:
             raise ValueError(f"num_heads {self.nq} is not a multiple of num_kv_heads {self.nkv}")
-        if self.d > 256:
-            raise ValueError(f"head_dim {self.d} exceeds what the attention kernels take (256)")
+        if self.d > 512:
+            raise ValueError(f"head size {self.d} exceeds what the attention kernels take (512)")
+        if self.dk != self.dv and self.norm_mode:
+            raise ValueError("a QK norm over heads that are filled up to the value size is not offered")
         pos_spec = p["position"]
         self.position = POSITIONS.get(pos_spec.kind)(pos_spec, prefix)
         scope = p["scope"]
@@ -150,7 +164,11 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
         self.n_qnorm = f"{self.scope}.{names['q_norm']}"
         self.n_knorm = f"{self.scope}.{names['k_norm']}"
         self._split = [f"{self.scope}.{names[k]}" for k in ("q", "k", "v")]
-        self.w_qkv = self.w_o = self.w_qnorm = self.w_knorm = None
+        self.w_qkv = self.w_o = self.w_qnorm = self.w_knorm = self.b_qkv = self.b_o = None
+        if self.has_bias:
+            self.n_qkv_bias = f"{self.scope}.{names['qkv_bias']}"
+            self.n_o_bias = f"{self.scope}.{names['o_bias']}"
+            self._split_bias = [f"{self.scope}.{names[k]}" for k in ("q_bias", "k_bias", "v_bias")]
 
     def children(self):
         return [self.position]
@@ -160,14 +178,19 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
         return PagedKVNeed(self.nkv, self.d, self.window)
 
     def tensor_specs(self) -> List[TensorSpec]:
-        qn, kn = self.nq * self.d, self.nkv * self.d
+        qn, kn, vn = self.nq * self.dk, self.nkv * self.dk, self.nkv * self.dv
         specs = [
-            TensorSpec(self.n_qkv, (qn + 2 * kn, self.hidden), sources=(Cat((
+            TensorSpec(self.n_qkv, (qn + kn + vn, self.hidden), sources=(Cat((
                 Name(self._split[0], (qn, self.hidden)),
                 Name(self._split[1], (kn, self.hidden)),
-                Name(self._split[2], (kn, self.hidden))), 0),)),
-            TensorSpec(self.n_o, (self.hidden, qn), tag="residual_out"),
+                Name(self._split[2], (vn, self.hidden))), 0),)),
+            TensorSpec(self.n_o, (self.hidden, self.nq * self.dv), tag="residual_out"),
         ]
+        if self.has_bias:
+            specs.append(TensorSpec(self.n_qkv_bias, (qn + kn + vn,), role="small32", tag="bias", sources=(Cat((
+                Name(self._split_bias[0], (qn,)), Name(self._split_bias[1], (kn,)),
+                Name(self._split_bias[2], (vn,))), 0),)))
+            specs.append(TensorSpec(self.n_o_bias, (self.hidden,), role="small32", tag="bias"))
         if self.norm_mode:
             sizes = (qn, kn) if self.norm_mode == 1 else (self.d, self.d)
             mean = 0.0 if self.norm_plus_one else 1.0
@@ -176,22 +199,43 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
                                         init=Init(mean=mean, std=0.0), tag="norm"))
         return specs
 
+    def _filled(self, t: torch.Tensor, heads_and_sizes, axis: int) -> torch.Tensor:
+        """``t`` with every head along ``axis`` filled up with zeros to the kernels' head size;
+        ``heads_and_sizes``: (heads, size) of the runs of heads along the axis, in order."""
+        if all(size == self.d for _, size in heads_and_sizes):
+            return t
+        pieces, at = [], 0
+        for heads, size in heads_and_sizes:
+            run = t.narrow(axis, at, heads * size)
+            at += heads * size
+            shape = list(run.shape)
+            shape[axis:axis + 1] = [heads, size]
+            run = run.reshape(shape)
+            pad = list(run.shape)
+            pad[axis + 1] = self.d - size
+            pieces.append(torch.cat((run, run.new_zeros(pad)), axis + 1).flatten(axis, axis + 1))
+        return torch.cat(pieces, axis).contiguous()
+
     def bind(self, tensors: Dict[str, torch.Tensor], dtype) -> None:
-        self.w_qkv = tensors[self.n_qkv]
-        self.w_o = tensors[self.n_o]
+        runs = ((self.nq, self.dk), (self.nkv, self.dk), (self.nkv, self.dv))
+        self.w_qkv = self._filled(tensors[self.n_qkv], runs, 0)
+        self.w_o = self._filled(tensors[self.n_o], ((self.nq, self.dv),), 1)
+        if self.has_bias:
+            self.b_qkv = self._filled(tensors[self.n_qkv_bias], runs, 0)
+            self.b_o = tensors[self.n_o_bias]
         if self.norm_mode:
             self.w_qnorm = tensors[self.n_qnorm]
             self.w_knorm = tensors[self.n_knorm]
 
     def libraries(self, dtype) -> List[str]:
-        return ["elementwise"] + self.attention_libraries(dtype) + linear.libraries(dtype)
+        return ["elementwise"] + self.attention_libraries(dtype) + linear.libraries(dtype, self.has_bias)
 
     # ---- forward ----------------------------------------------------------------
-    def forward(self, ctx: StepContext, x: torch.Tensor, cache: CacheView) -> torch.Tensor:
+    def forward(self, ctx: StepContext, x: torch.Tensor, cache: CacheView, out=None) -> torch.Tensor:
         T = x.shape[0]
         ws = ctx.workspace
         qn, kn = self.nq * self.d, self.nkv * self.d
-        qkv = linear.linear(x, self.w_qkv, ws.get("attn.qkv", (T, qn + 2 * kn), ctx.dtype))
+        qkv = linear.linear(x, self.w_qkv, ws.get("attn.qkv", (T, qn + 2 * kn), ctx.dtype), bias=self.b_qkv)
         q = ws.get("attn.q", (T, qn), ctx.dtype)
         table = ctx.block_tables[cache.block_table_index]
         cos_sin = self.position.table(ctx.device, ctx.max_positions)
@@ -202,4 +246,6 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
             self.position.interleaved, self.norm_eps)
         o = ws.get("attn.o", (T, qn), ctx.dtype)
         self.attend(ctx, q, o, cache.kv_pages, table)
-        return linear.linear(o, self.w_o, ws.get("attn.y", (T, self.hidden), ctx.dtype))
+        if out is None:
+            out = ws.get("attn.y", (T, self.hidden), ctx.dtype)
+        return linear.linear(o, self.w_o, out, bias=self.b_o)

@@ -19,6 +19,17 @@ sum of their outputs::
 The two outputs leave the block as ``[T, 2, H]``; the next norm adds them to each
 other and then to the residual in float32 (``x + (mixer + feed_forward)``).  A
 parallel layer may have no feed-forward; then it returns the mixer's rows alone.
+
+``sandwich`` norms every sublayer's output as well as its input and scales it before it
+joins the residual stream::
+
+    h = norm_in(delta, residual)                  # residual += delta
+    residual += mult * norm_out(mixer(h))
+    residual += mult * norm_out'(feed_forward(norm_in'(residual)))
+
+Both sums happen in float32 inside the norm kernel that computes the output norm; the
+output norm of the mixer and the input norm of the feed-forward are one launch.  The
+block leaves nothing pending (it returns ``None``).
 """
 
 from __future__ import annotations
@@ -64,3 +75,33 @@ class ParallelBlock(Block):
         else:
             pair[:, 1].copy_(self.feed_forward.forward(ctx, h))
         return pair
+
+
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """params: ``residual_mult`` (default 1): the factor on every normed sublayer output."""
+
+    NORM_NAMES = ("mixer", "mixer_out", "feed_forward", "feed_forward_out")
+    HAS_FEED_FORWARD = True          # or none: then only the mixer's two norms
+
+    @classmethod
+    def check_parts(cls, prefix, norm_names, has_feed_forward) -> None:
+        want = cls.NORM_NAMES if has_feed_forward else cls.NORM_NAMES[:2]
+        if sorted(norm_names) != sorted(want):
+            raise ValueError(f"layer '{prefix}': a sandwich block {'with' if has_feed_forward else 'without'} "
+                             f"feed-forward has the norms {list(want)}, the layer lists {sorted(norm_names)}")
+
+    def __init__(self, spec, prefix, mixer, feed_forward, norms):
+        super().__init__(spec, prefix, mixer, feed_forward, norms)
+        self.mult = float(spec.get("residual_mult", 1.0))
+
+    def forward(self, ctx, delta, residual, cache):
+        h = self.norms["mixer"].forward(ctx, delta, residual)
+        a = self.mixer.forward(ctx, h, cache)
+        if self.feed_forward is None:
+            self.norms["mixer_out"].add_normed(ctx, a, residual, self.mult)
+            return None
+        h = self.norms["mixer_out"].add_normed(ctx, a, residual, self.mult, then=self.norms["feed_forward"])
+        f = self.feed_forward.forward(ctx, h)
+        self.norms["feed_forward_out"].add_normed(ctx, f, residual, self.mult)
+        return None

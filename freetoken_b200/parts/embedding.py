@@ -63,7 +63,8 @@ class TokenEmbedding(Embedding):
 
 @register_head("lm_head")
 class LMHead(Head):
-    """params: ``vocab_size, hidden_size, scope``, ``tied_to`` (full name of
+    """params: ``vocab_size, hidden_size, scope`` (the tensor is ``<scope>.weight``) or ``tensor``
+    (its whole name), ``tied_to`` (full name of
     the embedding table, or None; a tied head with no ``scope`` has no tensor of its own,
     not even an optional one), ``softcap`` (None or 0: no cap on the logits)."""
 
@@ -75,9 +76,11 @@ class LMHead(Head):
         self.hidden = int(spec.params["hidden_size"])
         self.tied_to = spec.get("tied_to")
         scope = spec.get("scope")
-        if not scope and not self.tied_to:
-            raise ValueError("a head needs a tensor of its own ('scope') or a table to share ('tied_to')")
-        self.own_name = self.name(f"{scope}.weight") if scope else None
+        own = spec.get("tensor") or (f"{scope}.weight" if scope else None)
+        if not own and not self.tied_to:
+            raise ValueError("a head needs a tensor of its own ('scope' or 'tensor') or a table to share "
+                             "('tied_to')")
+        self.own_name = self.name(own) if own else None
         self.weight_name = self.tied_to or self.own_name
         self.softcap = float(spec.get("softcap") or 0.0)
         self.weight = None

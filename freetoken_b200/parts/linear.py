@@ -24,11 +24,25 @@ from ..csrc import ops
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-           activation: Optional[str] = None) -> torch.Tensor:
+           activation: Optional[str] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = f(x @ weight^T)``; ``weight`` is ``[N, K]``; ``out`` preallocated.  ``activation``
     names ``f`` (one of ``ops.ACTIVATIONS``; ``None``: the product itself): the weight-streaming
     kernel applies it to its float32 accumulator, behind the other products it is a launch
-    of its own on the stored result."""
+    of its own on the stored result.  ``bias`` (float32 ``[N]``; not together with an
+    activation) is added to the product: by the library product itself where that runs (its
+    float32 accumulator plus the bias, rounded once), by a launch of its own elsewhere."""
+    if bias is not None:
+        if activation is not None:
+            raise ValueError("linear: a bias and an activation together are not offered")
+        rows = x.shape[0]
+        if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+                and out.is_contiguous()
+                and not (rows <= SKINNY_ROWS and ops.skinny_gemm_takes(x, weight, out))):
+            torch.addmm(_bias_as(bias, torch.bfloat16), x, weight.t(), out=out)
+            return out
+        linear(x, weight, out)
+        ops.bias_add(out, bias)
+        return out
     if activation is not None:
         if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_ROWS
                 and ops.skinny_gemm_takes(x, weight, out)):
@@ -53,6 +67,20 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
             return out
     ops.gemm_rows(x, weight, out)
     return out
+
+
+_BIAS_COPIES = {}
+
+
+def _bias_as(bias: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 bias in the library product's element type (made once per bias; exact for a
+    bias that was stored in that type)."""
+    key = (bias.data_ptr(), dtype)
+    hit = _BIAS_COPIES.get(key)
+    if hit is None or hit[0] is not bias:
+        hit = (bias, bias.to(dtype))
+        _BIAS_COPIES[key] = hit
+    return hit[1]
 
 
 _F32_OUT = {"ok": None}
@@ -87,5 +115,6 @@ def library_f32_out(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) ->
 SKINNY_ROWS = 32
 
 
-def libraries(compute: torch.dtype) -> list:
-    return ["gemm_simt"] if compute == torch.float32 else ["gemm_simt", "skinny_gemm"]
+def libraries(compute: torch.dtype, bias: bool = False) -> list:
+    libs = ["gemm_simt"] if compute == torch.float32 else ["gemm_simt", "skinny_gemm"]
+    return libs + (["rowwise"] if bias else [])

@@ -42,9 +42,22 @@ class RMSNorm(Norm):
         self.weight = tensors[self.weight_name]
 
     def libraries(self, dtype) -> List[str]:
-        return ["elementwise"]
+        return ["elementwise", "rowwise"]
 
     def forward(self, ctx: StepContext, delta, residual: torch.Tensor) -> torch.Tensor:
         out = ctx.workspace.get("norm.out", residual.shape, ctx.dtype)
         ops.rmsnorm(delta, residual, self.weight, out, self.eps, self.plus_one)
+        return out
+
+    def add_normed(self, ctx: StepContext, branch: torch.Tensor, residual: torch.Tensor, mult: float,
+                   then: Optional["RMSNorm"] = None) -> Optional[torch.Tensor]:
+        """``residual += mult * norm(branch)`` in float32, this norm being the branch's own
+        (``branch`` is ``[T, H]`` or ``[T, k, H]`` partial rows, summed first).  With ``then`` the
+        new residual rows are normed by that norm in the same launch and returned."""
+        if then is None:
+            ops.norm_add(branch, residual, self.weight, self.eps, self.plus_one, mult)
+            return None
+        out = ctx.workspace.get("norm.out", residual.shape, ctx.dtype)
+        ops.norm_add(branch, residual, self.weight, self.eps, self.plus_one, mult, next_weight=then.weight,
+                     next_eps=then.eps, next_plus_one=then.plus_one, next_out=out)
         return out

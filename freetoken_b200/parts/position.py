@@ -20,20 +20,24 @@ from .base import Position, register_position
 # One cos|sin table per (rotary_dim, theta, device), shared by every layer that
 # rotates the same way (the reference shares one module through a cached
 # ``get_rope``, python/freetoken/layers/rotary.py:212-213).  A table only grows.
-_TABLES: Dict[Tuple[int, float, torch.device], torch.Tensor] = {}
+_TABLES: Dict[Tuple[int, float, torch.device, bool], torch.Tensor] = {}
 
 
-def rotary_table(rotary_dim: int, theta: float, device, positions: int) -> torch.Tensor:
+def rotary_table(rotary_dim: int, theta: float, device, positions: int, exact_angles: bool = False) -> torch.Tensor:
     """``[>= positions, rotary_dim]`` float32 on ``device``: ``cos | sin`` of
-    ``position * theta^(-2i/rotary_dim)``, computed on the host in float32."""
-    key = (int(rotary_dim), float(theta), torch.device(device))
+    ``position * theta^(-2i/rotary_dim)``, computed on the host in float32; with
+    ``exact_angles`` the angle, its cosine and sine are computed in float64 and rounded once,
+    so that the float32 product ``position * frequency`` (half a unit in the last place of the
+    angle, 3e-5 rad at position 1,000) does not enter."""
+    key = (int(rotary_dim), float(theta), torch.device(device), bool(exact_angles))
     table = _TABLES.get(key)
     if table is None or table.shape[0] < positions:
         r = int(rotary_dim)
-        inv_freq = 1.0 / (float(theta) ** (torch.arange(0, r, 2, dtype=torch.float) / r))
-        t = torch.arange(positions, dtype=torch.float)
+        real = torch.float64 if exact_angles else torch.float
+        inv_freq = 1.0 / (float(theta) ** (torch.arange(0, r, 2, dtype=real) / r))
+        t = torch.arange(positions, dtype=real)
         freqs = torch.einsum("i,j -> ij", t, inv_freq)
-        table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(device)
+        table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).float().contiguous().to(device)
         _TABLES[key] = table
     return table
 
@@ -48,6 +52,7 @@ class _Rotary(Position):
         self.rotary_dim = int(spec.params["rotary_dim"])
         self.theta = float(spec.params["theta"])
         self.max_position = int(spec.params["max_position"])
+        self.exact_angles = bool(spec.params.get("exact_angles", False))
         if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and within head_dim {self.head_dim}")
 
@@ -56,7 +61,8 @@ class _Rotary(Position):
         nothing rotates); every layer with the same rotation gets the same tensor."""
         if self.rotary_dim == 0:
             return None
-        return rotary_table(self.rotary_dim, self.theta, device, min(positions, self.max_position))
+        return rotary_table(self.rotary_dim, self.theta, device, min(positions, self.max_position),
+                            self.exact_angles)
 
 
 @register_position("rotary_neox")
