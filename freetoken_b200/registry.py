@@ -100,3 +100,12 @@ def _load_builtin() -> None:
             config_to_dict=lambda cfg: cfg.to_dict(),
         ),
     )
+    from .config import tonapel
+    register_architecture(
+        Architecture(
+            name=tonapel.ARCHITECTURE,
+            read_config=tonapel.TonapelConfig.from_dict,
+            build_plan=tonapel.build_plan,
+            config_to_dict=lambda cfg: cfg.to_dict(),
+        ),
+    )
