@@ -89,6 +89,23 @@ def window_attention(h, p, W, c):
     return out.reshape(T, H * DV) @ W[p + "o"].T + W[p + "o.b"]
 
 
+def ssd_recurrence(x, B, C, dt, dt_bias, A_log, D, S=None):
+    """``x`` ``[T, heads, P]``, ``B``/``C`` ``[T, groups, N]``, ``dt`` ``[T, heads]`` (before its bias and
+    softplus); the state ``S`` ``[heads, N, P]`` starts at zero and is returned updated in place."""
+    T, Hh, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    dt = softplus(dt + dt_bias)
+    A = -torch.exp(A_log)
+    y = torch.zeros(T, Hh, P, dtype=x.dtype)
+    S = torch.zeros(Hh, N, P, dtype=x.dtype) if S is None else S
+    for t in range(T):
+        for head in range(Hh):
+            g = head // (Hh // G)
+            S[head] = torch.exp(A[head] * dt[t, head]) * S[head] + dt[t, head] * torch.outer(B[t, g], x[t, head])
+            y[t, head] = S[head].T @ C[t, g] + D[head] * x[t, head]
+    return y
+
+
 def ssd(h, p, W, c, eps):
     """Right half: a selective state space of one decay per head."""
     T = h.shape[0]
@@ -100,15 +117,7 @@ def ssd(h, p, W, c, eps):
     x = xbc[:, :inner].view(T, Hh, P)
     B = xbc[:, inner:inner + G * N].view(T, G, N)
     C = xbc[:, inner + G * N:].view(T, G, N)
-    dt = softplus(dt + W[p + "dt_bias"])
-    A = -torch.exp(W[p + "A_log"])
-    y = torch.zeros(T, Hh, P, dtype=h.dtype)
-    S = torch.zeros(Hh, N, P, dtype=h.dtype)
-    for t in range(T):
-        for head in range(Hh):
-            g = head // (Hh // G)
-            S[head] = torch.exp(A[head] * dt[t, head]) * S[head] + dt[t, head] * torch.outer(B[t, g], x[t, head])
-            y[t, head] = S[head].T @ C[t, g] + W[p + "D"][head] * x[t, head]
+    y = ssd_recurrence(x, B, C, dt, W[p + "dt_bias"], W[p + "A_log"], W[p + "D"])
     y = y.reshape(T, inner) * silu(z)
     parts = c["norm_groups"]
     y = rms(y.view(T, parts, inner // parts), eps).reshape(T, inner) * W[p + "norm"]
@@ -120,19 +129,17 @@ def parallel_mixer(h, p, W, c, eps):
             + c["right_scale"] * ssd(h, p + "right.", W, c["right"], eps))
 
 
-def delta_mixer(h, p, W, c, eps):
-    """Gated delta rule: the state forgets by g, then is corrected toward v along k."""
-    T = h.shape[0]
-    Hh, G, D, DV = c["heads"], c["kv_heads"], c["dim"], c["vdim"]
-    q = silu(causal_conv(h @ W[p + "q"].T, W[p + "q.conv"])).view(T, G, D)
-    k = silu(causal_conv(h @ W[p + "k"].T, W[p + "k.conv"])).view(T, G, D)
-    v = silu(causal_conv(h @ W[p + "v"].T, W[p + "v.conv"])).view(T, Hh, DV)
-    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
-    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-    beta = torch.sigmoid(h @ W[p + "b"].T)
-    g = torch.exp(-torch.exp(W[p + "A_log"]) * softplus(h @ W[p + "a"].T + W[p + "dt_bias"]))
-    o = torch.zeros(T, Hh, DV, dtype=h.dtype)
-    S = torch.zeros(Hh, D, DV, dtype=h.dtype)
+def delta_recurrence(q, k, v, beta, decay, dt_bias, A_log, S=None, unit_eps=1e-6):
+    """``q``/``k`` ``[T, key heads, D]`` and ``v`` ``[T, heads, P]`` after their convolutions; ``beta`` and
+    ``decay`` ``[T, heads]`` as projected.  The state ``S`` ``[heads, D, P]`` starts at zero."""
+    T, Hh, DV = v.shape
+    G, D = q.shape[1], q.shape[2]
+    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * D ** -0.5
+    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+    beta = torch.sigmoid(beta)
+    g = torch.exp(-torch.exp(A_log) * softplus(decay + dt_bias))
+    o = torch.zeros(T, Hh, DV, dtype=v.dtype)
+    S = torch.zeros(Hh, D, DV, dtype=v.dtype) if S is None else S
     for t in range(T):
         for head in range(Hh):
             kv = head // (Hh // G)
@@ -140,6 +147,17 @@ def delta_mixer(h, p, W, c, eps):
             u = beta[t, head] * (v[t, head] - S[head].T @ k[t, kv])
             S[head] = S[head] + torch.outer(k[t, kv], u)
             o[t, head] = S[head].T @ q[t, kv]
+    return o
+
+
+def delta_mixer(h, p, W, c, eps):
+    """Gated delta rule: the state forgets by g, then is corrected toward v along k."""
+    T = h.shape[0]
+    Hh, G, D, DV = c["heads"], c["kv_heads"], c["dim"], c["vdim"]
+    q = silu(causal_conv(h @ W[p + "q"].T, W[p + "q.conv"])).view(T, G, D)
+    k = silu(causal_conv(h @ W[p + "k"].T, W[p + "k.conv"])).view(T, G, D)
+    v = silu(causal_conv(h @ W[p + "v"].T, W[p + "v.conv"])).view(T, Hh, DV)
+    o = delta_recurrence(q, k, v, h @ W[p + "b"].T, h @ W[p + "a"].T, W[p + "dt_bias"], W[p + "A_log"])
     o = rms(o, eps) * W[p + "norm"] * silu(h @ W[p + "g"].T).view(T, Hh, DV)
     return o.reshape(T, Hh * DV) @ W[p + "o"].T
 
