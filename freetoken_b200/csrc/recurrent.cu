@@ -19,7 +19,9 @@
 // State layout per head: [N or D][P] float32, P contiguous.  A warp owns WC
 // columns of a head's state and its lanes split the rows, so a column's dot
 // products are one warp reduction; a block's four warps share the tokens of a
-// chunk, which all threads stage into shared memory together.
+// chunk, which all threads stage into shared memory together.  Which WC a launch
+// takes depends on the step's shape, never on a token's place in it, and the
+// operations on a column are the same for every WC.
 #include "common.cuh"
 
 namespace ft {
@@ -64,8 +66,104 @@ struct ConvArgs {
   int C, taps;
 };
 
+constexpr int CONV_MAX_TAPS = 8;     // longer convolutions take the plain loop
+
+// A thread owns one channel (two neighbouring ones where rows allow 4-byte pieces of bfloat16)
+// and `run` consecutive tokens: while they belong to one segment it keeps the last taps inputs
+// in registers and fetches one new input a token; at a segment's first token (and always when
+// run is 1) it fetches the whole reach, from earlier rows or from the slot.  The sum runs over
+// ascending taps either way.
+template <typename AT, int CPT, int RUN>
+__global__ void __launch_bounds__(128) conv_silu_kernel(ConvArgs a, int T) {
+  constexpr int run = RUN;
+  pdl_wait();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * CPT;
+  if (c >= a.C) return;
+  const int K = a.taps - 1;
+  const AT* x = (const AT*)a.x;
+  float w[CPT][CONV_MAX_TAPS], win[CPT][CONV_MAX_TAPS], bias[CPT];
+#pragma unroll
+  for (int u = 0; u < CPT; ++u) {
+    bias[u] = a.bias ? a.bias[c + u] : 0.f;
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) w[u][j] = j <= K ? a.w[(size_t)(c + u) * a.taps + j] : 0.f;
+  }
+  auto fetch = [&](int row, float (&v)[CPT]) {          // CPT inputs of a token's row
+    if constexpr (CPT == 2) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + (size_t)row * a.ldx + c));
+      v[0] = f.x;
+      v[1] = f.y;
+    } else {
+      v[0] = to_float(x[(size_t)row * a.ldx + c]);
+    }
+  };
+  int prev_seg = -1;
+  const int t_first = blockIdx.x * run, t_end = min(T, (blockIdx.x + 1) * run);
+  // every token's own input and segment first, all loads in flight together
+  float own[RUN][CPT];
+  int segs[RUN];
+#pragma unroll
+  for (int i = 0; i < RUN; ++i) {
+    if (t_first + i < t_end) {
+      fetch(t_first + i, own[i]);
+      segs[i] = a.token_seg[t_first + i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RUN; ++i) {
+    const int t = t_first + i;
+    if (t >= t_end) break;
+    const int seg = segs[i];
+    const int q0 = a.seg_q_start[seg];
+    const int r = t - q0;
+    if (seg != prev_seg) {
+      const float* st = a.state + (size_t)a.seg_slot[seg] * a.slot_stride;
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+        if (j > K) break;
+        const int s = r - K + j;
+        float v[CPT];
+        if (s == r) {
+#pragma unroll
+          for (int u = 0; u < CPT; ++u) v[u] = own[i][u];
+        } else if (s >= 0) fetch(q0 + s, v);
+        else {
+#pragma unroll
+          for (int u = 0; u < CPT; ++u) v[u] = st[(size_t)(K + s) * a.C + c + u];
+        }
+#pragma unroll
+        for (int u = 0; u < CPT; ++u) win[u][j] = v[u];
+      }
+      prev_seg = seg;
+    } else {
+#pragma unroll
+      for (int u = 0; u < CPT; ++u) {
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+          if (j < K) win[u][j] = win[u][j + 1];
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j)
+          if (j == K) win[u][j] = own[i][u];
+      }
+    }
+    float out[CPT];
+#pragma unroll
+    for (int u = 0; u < CPT; ++u) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS; ++j)
+        if (j <= K) acc = fmaf(w[u][j], win[u][j], acc);
+      out[u] = silu_f(acc + bias[u]);
+    }
+    AT* o = (AT*)a.out + (size_t)t * a.ldo + c;
+    if constexpr (CPT == 2) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(out[0], out[1]);
+    else o[0] = from_float<AT>(out[0]);
+  }
+}
+
+// any number of taps: one channel and one token a thread
 template <typename AT>
-__global__ void __launch_bounds__(128) conv_silu_kernel(ConvArgs a) {
+__global__ void __launch_bounds__(128) conv_silu_long_kernel(ConvArgs a) {
   pdl_wait();
   const int t = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -103,10 +201,55 @@ __global__ void __launch_bounds__(128) conv_state_kernel(ConvArgs a) {
 }
 
 // -------------------------------------------------------- selective state space
+// Both scans share their shape.  A block of four warps owns COLS = 4 * WC columns of one head's
+// state in one segment; a warp owns WC of them and its lanes split the rows (NPL rows a lane).
+// Tokens come in chunks of SCAN_CHUNK: every thread fetches its share of the NEXT chunk's rows
+// into registers before the block works through the current chunk from shared memory, and puts
+// them into the other of two buffers afterwards, so that the loads' latency hides under the
+// arithmetic and a chunk costs one block-wide barrier.  A full chunk's tokens are unrolled, so
+// that the shuffles of one token's read-out overlap the next token's products.
 constexpr int SCAN_WARPS = 4;
-constexpr int SCAN_WC = 8;                       // state columns a warp owns
-constexpr int SCAN_COLS = SCAN_WARPS * SCAN_WC;  // ... a block owns
-constexpr int SCAN_CHUNK = 16;                   // tokens staged in shared memory at a time
+constexpr int SCAN_THREADS = SCAN_WARPS * 32;
+constexpr int SCAN_CHUNK = 8;
+
+// WC consecutive floats of a state row: 16- or 8-byte pieces when `vec` says they are aligned
+template <int WC>
+__device__ __forceinline__ void load_cols(const float* p, float (&v)[WC], int valid, bool vec) {
+  if (WC > 1 && vec && valid >= WC) {
+    if constexpr (WC % 4 == 0) {
+#pragma unroll
+      for (int c = 0; c < WC; c += 4) {
+        const float4 f = *reinterpret_cast<const float4*>(p + c);
+        v[c] = f.x; v[c + 1] = f.y; v[c + 2] = f.z; v[c + 3] = f.w;
+      }
+    } else if constexpr (WC % 2 == 0) {
+#pragma unroll
+      for (int c = 0; c < WC; c += 2) {
+        const float2 f = *reinterpret_cast<const float2*>(p + c);
+        v[c] = f.x; v[c + 1] = f.y;
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int c = 0; c < WC; ++c) v[c] = c < valid ? p[c] : 0.f;
+}
+template <int WC>
+__device__ __forceinline__ void store_cols(float* p, const float (&v)[WC], int valid, bool vec) {
+  if (WC > 1 && vec && valid >= WC) {
+    if constexpr (WC % 4 == 0) {
+#pragma unroll
+      for (int c = 0; c < WC; c += 4) *reinterpret_cast<float4*>(p + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+    } else if constexpr (WC % 2 == 0) {
+#pragma unroll
+      for (int c = 0; c < WC; c += 2) *reinterpret_cast<float2*>(p + c) = make_float2(v[c], v[c + 1]);
+    }
+    return;
+  }
+#pragma unroll
+  for (int c = 0; c < WC; ++c)
+    if (c < valid) p[c] = v[c];
+}
 
 struct SsdArgs {
   const void* xbc;      // [T, ld]: x (heads * P) | B (G * N) | C (G * N), after convolution and silu
@@ -120,11 +263,15 @@ struct SsdArgs {
   const int* seg_q_start;
   long long ld, ld_dt, slot_stride;
   int heads, P, N, G;
+  int vec;              // state rows may be read in 16-byte (WC % 4 == 0) or 8-byte pieces
 };
 
-// NPL: state rows a lane holds (N <= 32 * NPL)
-template <typename AT, int NPL>
-__global__ void __launch_bounds__(SCAN_WARPS * 32) ssd_scan_kernel(SsdArgs a) {
+// NPL: state rows a lane holds (N <= 32 * NPL); WC: state columns a warp owns
+template <typename AT, int NPL, int WC>
+__global__ void __launch_bounds__(SCAN_THREADS) ssd_scan_kernel(SsdArgs a) {
+  constexpr int COLS = SCAN_WARPS * WC;
+  constexpr int NB = (NPL * 32 + SCAN_THREADS - 1) / SCAN_THREADS;       // B (or C) values a thread stages per token
+  constexpr int XR = (SCAN_CHUNK * COLS + SCAN_THREADS - 1) / SCAN_THREADS;
   extern __shared__ float sm[];
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -132,48 +279,89 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) ssd_scan_kernel(SsdArgs a) {
   const int N = a.N, P = a.P;
   const int g = head / (a.heads / a.G);
   const int inner = a.heads * P;
-  const int col0 = blockIdx.x * SCAN_COLS;           // first column of the block
-  const int j0 = col0 + warp * SCAN_WC;              // first column of the warp
-  float* Bs = sm;                                     // [CHUNK][N]
-  float* Cs = Bs + SCAN_CHUNK * N;                    // [CHUNK][N]
-  float* xs = Cs + SCAN_CHUNK * N;                    // [CHUNK][SCAN_COLS]
-  float* dts = xs + SCAN_CHUNK * SCAN_COLS;           // [CHUNK] step size
-  float* das = dts + SCAN_CHUNK;                      // [CHUNK] decay
+  const int col0 = blockIdx.x * COLS;
+  const int j0 = col0 + warp * WC;
+  const int per = SCAN_CHUNK * (2 * N + COLS + 2);                         // floats of one buffer
   const int q0 = a.seg_q_start[seg], q1 = a.seg_q_start[seg + 1];
   float* st = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + (size_t)head * N * P;
   const float rate = -expf(a.A_log[head]), bias = a.dt_bias[head], skip = a.D[head];
+  const AT* xbc = (const AT*)a.xbc;
+  const AT* dt = (const AT*)a.dt;
 
-  float S[NPL][SCAN_WC];
+  float S[NPL][WC];
 #pragma unroll
   for (int e = 0; e < NPL; ++e) {
     const int n = lane + 32 * e;
+    if (n < N) load_cols<WC>(st + (size_t)n * P + j0, S[e], P - j0, a.vec);
+    else {
 #pragma unroll
-    for (int c = 0; c < SCAN_WC; ++c)
-      S[e][c] = (n < N && j0 + c < P) ? st[(size_t)n * P + j0 + c] : 0.f;
+      for (int c = 0; c < WC; ++c) S[e][c] = 0.f;
+    }
   }
-  const AT* xbc = (const AT*)a.xbc;
-  const AT* dt = (const AT*)a.dt;
-  for (int t0 = q0; t0 < q1; t0 += SCAN_CHUNK) {
-    const int nt = min(SCAN_CHUNK, q1 - t0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
-      const int tt = i / N, n = i % N;
-      const AT* row = xbc + (size_t)(t0 + tt) * a.ld + inner + (size_t)g * N + n;
-      Bs[tt * N + n] = to_float(row[0]);
-      Cs[tt * N + n] = to_float(row[(size_t)a.G * N]);
+
+  AT pb[SCAN_CHUNK][NB], pc[SCAN_CHUNK][NB], px[XR], pdt;
+  auto fetch = [&](int t0, int nt) {
+#pragma unroll
+    for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const int n = threadIdx.x + SCAN_THREADS * b;
+        if (tt < nt && n < N) {
+          const AT* row = xbc + (size_t)(t0 + tt) * a.ld + inner + (size_t)g * N + n;
+          pb[tt][b] = row[0];
+          pc[tt][b] = row[(size_t)a.G * N];
+        }
+      }
     }
-    for (int i = threadIdx.x; i < nt * SCAN_COLS; i += blockDim.x) {
-      const int tt = i / SCAN_COLS, c = i % SCAN_COLS;
-      xs[i] = col0 + c < P ? to_float(xbc[(size_t)(t0 + tt) * a.ld + (size_t)head * P + col0 + c]) : 0.f;
+#pragma unroll
+    for (int r = 0; r < XR; ++r) {
+      const int i = threadIdx.x + SCAN_THREADS * r, tt = i / COLS, c = i % COLS;
+      px[r] = (tt < nt && col0 + c < P) ? xbc[(size_t)(t0 + tt) * a.ld + (size_t)head * P + col0 + c] : from_float<AT>(0.f);
     }
-    if (threadIdx.x < nt) {
-      const float step = softplus_f(to_float(dt[(size_t)(t0 + threadIdx.x) * a.ld_dt + head]) + bias);
+    if ((int)threadIdx.x < nt) pdt = dt[(size_t)(t0 + threadIdx.x) * a.ld_dt + head];
+  };
+  auto put = [&](float* buf, int nt) {
+    float* Bs = buf;
+    float* Cs = Bs + SCAN_CHUNK * N;
+    float* xs = Cs + SCAN_CHUNK * N;
+    float* dts = xs + SCAN_CHUNK * COLS;
+#pragma unroll
+    for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const int n = threadIdx.x + SCAN_THREADS * b;
+        if (tt < nt && n < N) {
+          Bs[tt * N + n] = to_float(pb[tt][b]);
+          Cs[tt * N + n] = to_float(pc[tt][b]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < XR; ++r) {
+      const int i = threadIdx.x + SCAN_THREADS * r;
+      if (i < SCAN_CHUNK * COLS) xs[i] = to_float(px[r]);
+    }
+    if ((int)threadIdx.x < nt) {
+      const float step = softplus_f(to_float(pdt) + bias);
       dts[threadIdx.x] = step;
-      das[threadIdx.x] = expf(rate * step);
+      dts[SCAN_CHUNK + threadIdx.x] = expf(rate * step);
     }
-    __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float step = dts[tt], decay = das[tt];
+  };
+
+  fetch(q0, min(SCAN_CHUNK, q1 - q0));
+  put(sm, min(SCAN_CHUNK, q1 - q0));
+  __syncthreads();
+  int turn = 0;
+  for (int t0 = q0; t0 < q1; t0 += SCAN_CHUNK, turn ^= 1) {
+    const int nt = min(SCAN_CHUNK, q1 - t0);
+    const int next = min(SCAN_CHUNK, q1 - t0 - SCAN_CHUNK);
+    if (next > 0) fetch(t0 + SCAN_CHUNK, next);
+    const float* Bs = sm + turn * per;
+    const float* Cs = Bs + SCAN_CHUNK * N;
+    const float* xs = Cs + SCAN_CHUNK * N;
+    const float* dts = xs + SCAN_CHUNK * COLS;
+    auto token = [&](int tt) {
+      const float step = dts[tt], decay = dts[SCAN_CHUNK + tt];
       float Bv[NPL], Cv[NPL];
 #pragma unroll
       for (int e = 0; e < NPL; ++e) {
@@ -181,11 +369,11 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) ssd_scan_kernel(SsdArgs a) {
         Bv[e] = n < N ? Bs[tt * N + n] : 0.f;
         Cv[e] = n < N ? Cs[tt * N + n] : 0.f;
       }
-      float part[SCAN_WC];
+      float part[WC], xv[WC];
 #pragma unroll
-      for (int c = 0; c < SCAN_WC; ++c) {
-        const float xv = xs[tt * SCAN_COLS + warp * SCAN_WC + c];
-        const float in = step * xv;
+      for (int c = 0; c < WC; ++c) {
+        xv[c] = xs[tt * COLS + warp * WC + c];
+        const float in = step * xv[c];
         float acc = 0.f;
 #pragma unroll
         for (int e = 0; e < NPL; ++e) {
@@ -194,19 +382,28 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) ssd_scan_kernel(SsdArgs a) {
         }
         part[c] = acc;
       }
-      warp_sum_multi<SCAN_WC>(part);
-      const int c = lane >> (5 - Log2<SCAN_WC>::value);
-      if ((lane & ((32 / SCAN_WC) - 1)) == 0 && j0 + c < P)
-        a.y[(size_t)(t0 + tt) * inner + (size_t)head * P + j0 + c] =
-            part[0] + skip * xs[tt * SCAN_COLS + warp * SCAN_WC + c];
+      warp_sum_multi<WC>(part);
+      const int c = lane >> (5 - Log2<WC>::value);
+      if ((lane & ((32 / WC) - 1)) == 0 && j0 + c < P) {
+        float mine = xv[0];
+#pragma unroll
+        for (int i = 1; i < WC; ++i) mine = c == i ? xv[i] : mine;
+        a.y[(size_t)(t0 + tt) * inner + (size_t)head * P + j0 + c] = part[0] + skip * mine;
+      }
+    };
+    if (nt == SCAN_CHUNK) {
+#pragma unroll
+      for (int tt = 0; tt < SCAN_CHUNK; ++tt) token(tt);
+    } else {
+      for (int tt = 0; tt < nt; ++tt) token(tt);
     }
+    if (next > 0) put(sm + (turn ^ 1) * per, next);
+    __syncthreads();
   }
 #pragma unroll
   for (int e = 0; e < NPL; ++e) {
     const int n = lane + 32 * e;
-#pragma unroll
-    for (int c = 0; c < SCAN_WC; ++c)
-      if (n < N && j0 + c < P) st[(size_t)n * P + j0 + c] = S[e][c];
+    if (n < N) store_cols<WC>(st + (size_t)n * P + j0, S[e], P - j0, a.vec);
   }
 }
 
@@ -224,96 +421,135 @@ struct DeltaArgs {
   long long ld, ld_gate, slot_stride;
   int heads, P, D, G;
   float unit_eps, q_scale;
+  int vec;
 };
 
-template <typename AT, int NPL>
-__global__ void __launch_bounds__(SCAN_WARPS * 32) delta_scan_kernel(DeltaArgs a) {
+template <typename AT, int NPL, int WC>
+__global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
+  constexpr int COLS = SCAN_WARPS * WC;
+  constexpr int NB = (NPL * 32 + SCAN_THREADS - 1) / SCAN_THREADS;
+  constexpr int XR = (SCAN_CHUNK * COLS + SCAN_THREADS - 1) / SCAN_THREADS;
   extern __shared__ float sm[];
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int head = blockIdx.y, seg = blockIdx.z;
   const int D = a.D, P = a.P;
   const int g = head / (a.heads / a.G);
-  const int col0 = blockIdx.x * SCAN_COLS;
-  const int j0 = col0 + warp * SCAN_WC;
+  const int col0 = blockIdx.x * COLS;
+  const int j0 = col0 + warp * WC;
   const int width = a.heads * P;
-  float* qs = sm;                                     // [CHUNK][D] unit q times q_scale
-  float* ks = qs + SCAN_CHUNK * D;                    // [CHUNK][D] unit k
-  float* vs = ks + SCAN_CHUNK * D;                    // [CHUNK][SCAN_COLS]
-  float* bs = vs + SCAN_CHUNK * SCAN_COLS;            // [CHUNK] beta
-  float* gs = bs + SCAN_CHUNK;                        // [CHUNK] decay
-  float* kqs = gs + SCAN_CHUNK;                       // [CHUNK] k . q
+  const int per = SCAN_CHUNK * (2 * D + COLS + 2);
   const int q0 = a.seg_q_start[seg], q1 = a.seg_q_start[seg + 1];
   float* st = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + (size_t)head * D * P;
   const float rate = -expf(a.A_log[head]), bias = a.dt_bias[head];
+  const AT* qkv = (const AT*)a.qkv;
 
-  float S[NPL][SCAN_WC];
+  float S[NPL][WC];
 #pragma unroll
   for (int e = 0; e < NPL; ++e) {
     const int n = lane + 32 * e;
+    if (n < D) load_cols<WC>(st + (size_t)n * P + j0, S[e], P - j0, a.vec);
+    else {
 #pragma unroll
-    for (int c = 0; c < SCAN_WC; ++c)
-      S[e][c] = (n < D && j0 + c < P) ? st[(size_t)n * P + j0 + c] : 0.f;
+      for (int c = 0; c < WC; ++c) S[e][c] = 0.f;
+    }
   }
-  const AT* qkv = (const AT*)a.qkv;
-  for (int t0 = q0; t0 < q1; t0 += SCAN_CHUNK) {
-    const int nt = min(SCAN_CHUNK, q1 - t0);
-    __syncthreads();
-    // a warp makes unit vectors of the q and k rows of every fourth token
-    for (int tt = warp; tt < nt; tt += SCAN_WARPS) {
-      const AT* qrow = qkv + (size_t)(t0 + tt) * a.ld + (size_t)g * D;
-      const AT* krow = qrow + (size_t)a.G * D;
-      float qv[NPL], kv[NPL], sq = 0.f, sk = 0.f;
+
+  AT pq[SCAN_CHUNK][NB], pk[SCAN_CHUNK][NB], pv[XR], pbeta, pdecay;
+  auto fetch = [&](int t0, int nt) {
 #pragma unroll
-      for (int e = 0; e < NPL; ++e) {
-        const int n = lane + 32 * e;
-        qv[e] = n < D ? to_float(qrow[n]) : 0.f;
-        kv[e] = n < D ? to_float(krow[n]) : 0.f;
-        sq = fmaf(qv[e], qv[e], sq);
-        sk = fmaf(kv[e], kv[e], sk);
-      }
-      const float iq = a.q_scale / sqrtf(warp_sum(sq) + a.unit_eps);
-      const float ik = 1.f / sqrtf(warp_sum(sk) + a.unit_eps);
-      float dot = 0.f;
+    for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
 #pragma unroll
-      for (int e = 0; e < NPL; ++e) {
-        const int n = lane + 32 * e;
-        qv[e] *= iq;
-        kv[e] *= ik;
-        dot = fmaf(qv[e], kv[e], dot);
-        if (n < D) {
-          qs[tt * D + n] = qv[e];
-          ks[tt * D + n] = kv[e];
+      for (int b = 0; b < NB; ++b) {
+        const int n = threadIdx.x + SCAN_THREADS * b;
+        if (tt < nt && n < D) {
+          const AT* row = qkv + (size_t)(t0 + tt) * a.ld + (size_t)g * D + n;
+          pq[tt][b] = row[0];
+          pk[tt][b] = row[(size_t)a.G * D];
         }
       }
-      dot = warp_sum(dot);
-      if (lane == 0) {
-        kqs[tt] = dot;
-        const size_t at = (size_t)(t0 + tt) * a.ld_gate + head;
-        bs[tt] = 1.f / (1.f + expf(-to_float(((const AT*)a.beta)[at])));
-        gs[tt] = expf(rate * softplus_f(to_float(((const AT*)a.decay)[at]) + bias));
+    }
+#pragma unroll
+    for (int r = 0; r < XR; ++r) {
+      const int i = threadIdx.x + SCAN_THREADS * r, tt = i / COLS, c = i % COLS;
+      pv[r] = (tt < nt && col0 + c < P)
+                  ? qkv[(size_t)(t0 + tt) * a.ld + 2 * (size_t)a.G * D + (size_t)head * P + col0 + c]
+                  : from_float<AT>(0.f);
+    }
+    if ((int)threadIdx.x < nt) {
+      const size_t at = (size_t)(t0 + threadIdx.x) * a.ld_gate + head;
+      pbeta = ((const AT*)a.beta)[at];
+      pdecay = ((const AT*)a.decay)[at];
+    }
+  };
+  auto put = [&](float* buf, int nt) {
+    float* qs = buf;
+    float* ks = qs + SCAN_CHUNK * D;
+    float* vs = ks + SCAN_CHUNK * D;
+    float* gates = vs + SCAN_CHUNK * COLS;
+#pragma unroll
+    for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const int n = threadIdx.x + SCAN_THREADS * b;
+        if (tt < nt && n < D) {
+          qs[tt * D + n] = to_float(pq[tt][b]);
+          ks[tt * D + n] = to_float(pk[tt][b]);
+        }
       }
     }
-    for (int i = threadIdx.x; i < nt * SCAN_COLS; i += blockDim.x) {
-      const int tt = i / SCAN_COLS, c = i % SCAN_COLS;
-      vs[i] = col0 + c < P
-                  ? to_float(qkv[(size_t)(t0 + tt) * a.ld + 2 * (size_t)a.G * D + (size_t)head * P + col0 + c])
-                  : 0.f;
+#pragma unroll
+    for (int r = 0; r < XR; ++r) {
+      const int i = threadIdx.x + SCAN_THREADS * r;
+      if (i < SCAN_CHUNK * COLS) vs[i] = to_float(pv[r]);
     }
-    __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float beta = bs[tt], decay = gs[tt], kq = kqs[tt];
+    if ((int)threadIdx.x < nt) {
+      gates[threadIdx.x] = 1.f / (1.f + expf(-to_float(pbeta)));
+      gates[SCAN_CHUNK + threadIdx.x] = expf(rate * softplus_f(to_float(pdecay) + bias));
+    }
+  };
+
+  fetch(q0, min(SCAN_CHUNK, q1 - q0));
+  put(sm, min(SCAN_CHUNK, q1 - q0));
+  __syncthreads();
+  int turn = 0;
+  for (int t0 = q0; t0 < q1; t0 += SCAN_CHUNK, turn ^= 1) {
+    const int nt = min(SCAN_CHUNK, q1 - t0);
+    const int next = min(SCAN_CHUNK, q1 - t0 - SCAN_CHUNK);
+    if (next > 0) fetch(t0 + SCAN_CHUNK, next);
+    const float* qs = sm + turn * per;
+    const float* ks = qs + SCAN_CHUNK * D;
+    const float* vs = ks + SCAN_CHUNK * D;
+    const float* gates = vs + SCAN_CHUNK * COLS;
+    auto token = [&](int tt) {
+      const float beta = gates[tt], decay = gates[SCAN_CHUNK + tt];
       float qv[NPL], kv[NPL];
+      // sums of squares of the raw q and k rows and their product: unit vectors without a pass of
+      // their own (every warp of the block forms them for itself; they do not wait for the state)
+      float unit[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int e = 0; e < NPL; ++e) {
         const int n = lane + 32 * e;
         qv[e] = n < D ? qs[tt * D + n] : 0.f;
         kv[e] = n < D ? ks[tt * D + n] : 0.f;
+        unit[0] = fmaf(qv[e], qv[e], unit[0]);
+        unit[1] = fmaf(kv[e], kv[e], unit[1]);
+        unit[2] = fmaf(qv[e], kv[e], unit[2]);
       }
-      // per column: a = S^T k and b = S^T q of the state before this token
-      float red[2 * SCAN_WC];
+      warp_sum_multi<4>(unit);
+      const float mine_u = unit[0];                       // lane l holds value l >> 3
+      const float iq = a.q_scale / sqrtf(__shfl_sync(0xffffffffu, mine_u, 0) + a.unit_eps);
+      const float ik = 1.f / sqrtf(__shfl_sync(0xffffffffu, mine_u, 8) + a.unit_eps);
+      const float kq = __shfl_sync(0xffffffffu, mine_u, 16) * iq * ik;
 #pragma unroll
-      for (int c = 0; c < SCAN_WC; ++c) {
+      for (int e = 0; e < NPL; ++e) {
+        qv[e] *= iq;
+        kv[e] *= ik;
+      }
+      // per column: S^T k and S^T q of the state before this token
+      float red[2 * WC];
+#pragma unroll
+      for (int c = 0; c < WC; ++c) {
         float sa = 0.f, sb = 0.f;
 #pragma unroll
         for (int e = 0; e < NPL; ++e) {
@@ -321,31 +557,38 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) delta_scan_kernel(DeltaArgs a
           sb = fmaf(S[e][c], qv[e], sb);
         }
         red[c] = sa;
-        red[SCAN_WC + c] = sb;
+        red[WC + c] = sb;
       }
-      warp_sum_multi<2 * SCAN_WC>(red);
-      // lane l holds the total of value l >> 1: even pairs of lanes a_c, the upper half b_c
+      warp_sum_multi<2 * WC>(red);
+      constexpr int SHIFT = 5 - Log2<2 * WC>::value;      // lane l holds the total of value l >> SHIFT
       const float mine = red[0];
 #pragma unroll
-      for (int c = 0; c < SCAN_WC; ++c) {
-        const float sa = __shfl_sync(0xffffffffu, mine, 2 * c);
-        const float sb = __shfl_sync(0xffffffffu, mine, 2 * (SCAN_WC + c));
-        const float v = vs[tt * SCAN_COLS + warp * SCAN_WC + c];
-        // after the decay the state reads g a; the write u = beta (v - g a); the read-out sees it
+      for (int c = 0; c < WC; ++c) {
+        const float sa = __shfl_sync(0xffffffffu, mine, c << SHIFT);
+        const float sb = __shfl_sync(0xffffffffu, mine, (WC + c) << SHIFT);
+        const float v = vs[tt * COLS + warp * WC + c];
+        // the decayed state answers k with decay * sa; the token writes u along k, and its own
+        // read-out already contains that write: decay * sb + (k . q) u
         const float u = beta * (v - decay * sa);
         if (lane == 0 && j0 + c < P)
           a.o[(size_t)(t0 + tt) * width + (size_t)head * P + j0 + c] = fmaf(kq, u, decay * sb);
 #pragma unroll
         for (int e = 0; e < NPL; ++e) S[e][c] = fmaf(kv[e], u, decay * S[e][c]);
       }
+    };
+    if (nt == SCAN_CHUNK) {
+#pragma unroll
+      for (int tt = 0; tt < SCAN_CHUNK; ++tt) token(tt);
+    } else {
+      for (int tt = 0; tt < nt; ++tt) token(tt);
     }
+    if (next > 0) put(sm + (turn ^ 1) * per, next);
+    __syncthreads();
   }
 #pragma unroll
   for (int e = 0; e < NPL; ++e) {
     const int n = lane + 32 * e;
-#pragma unroll
-    for (int c = 0; c < SCAN_WC; ++c)
-      if (n < D && j0 + c < P) st[(size_t)n * P + j0 + c] = S[e][c];
+    if (n < D) store_cols<WC>(st + (size_t)n * P + j0, S[e], P - j0, a.vec);
   }
 }
 
@@ -384,21 +627,99 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(const float* __restrict
   }
 }
 
-template <typename AT, int NPL>
-static int launch_ssd(const SsdArgs& a, int S, cudaStream_t stream) {
-  const size_t smem = (size_t)(SCAN_CHUNK * (2 * a.N + SCAN_COLS) + 2 * SCAN_CHUNK) * sizeof(float);
+// The same norm with TPI threads per (token, group), 16-byte pieces, and every value kept in
+// registers between the sum of squares and the scaling: parts of up to 4 * KEEP * TPI values, a
+// multiple of 4, rows 16-byte (bfloat16 gate: 8-byte) aligned.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename AT, int TPI, int KEEP>
+__global__ void __launch_bounds__(128) gated_norm_vec_kernel(const float* __restrict__ y, const AT* __restrict__ z,
+                                                             long long ldz, const float* __restrict__ weight,
+                                                             int weight_len, AT* __restrict__ out, int T, int width,
+                                                             int groups, float eps, int gate_first) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  const int sub = threadIdx.x % TPI;
+  const long long item = (long long)blockIdx.x * (128 / TPI) + threadIdx.x / TPI;
+  if (item >= (long long)T * groups) return;          // a warp (TPI 32) or the whole block (TPI 128) leaves
+  const int t = (int)(item / groups), grp = (int)(item % groups);
+  const int size = width / groups, base = grp * size, pieces = size >> 2;
+  const float* row = y + (size_t)t * width + base;
+  const AT* gate = z + (size_t)t * ldz + base;
+  float4 keep[KEEP], gk[KEEP];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const int gi = sub + j * TPI;
+    if (gi < pieces) {
+      float4 v = ld4(row + 4 * gi);
+      const float4 gr = ld4(gate + 4 * gi);
+      const float4 gv = make_float4(silu_f(gr.x), silu_f(gr.y), silu_f(gr.z), silu_f(gr.w));
+      if (gate_first) { v.x *= gv.x; v.y *= gv.y; v.z *= gv.z; v.w *= gv.w; }
+      keep[j] = v;
+      gk[j] = gv;
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+  }
+  ss = TPI == 32 ? warp_sum(ss) : block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)size + eps);
+  AT* dst = out + (size_t)t * width + base;
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const int gi = sub + j * TPI;
+    if (gi < pieces) {
+      const float4 w = ld4(weight + (base + 4 * gi) % weight_len);
+      float4 v = keep[j];
+      v.x *= inv * w.x; v.y *= inv * w.y; v.z *= inv * w.z; v.w *= inv * w.w;
+      if (!gate_first) { v.x *= gk[j].x; v.y *= gk[j].y; v.z *= gk[j].z; v.w *= gk[j].w; }
+      st4(dst + 4 * gi, v);
+    }
+  }
+}
+
+// A few segments of a long prompt leave most SMs without a block when a warp owns 8 columns:
+// then a warp owns 2 and four times as many blocks share the work.
+#ifndef NARROW_WC
+#define NARROW_WC 2
+#endif
+static bool narrow_warps(int P, int heads, int S) {
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return (long long)((P + 31) / 32) * heads * S < 2LL * sms;
+}
+
+template <typename AT, int NPL, int WC>
+static int launch_ssd(SsdArgs a, int S, cudaStream_t stream) {
+  constexpr int COLS = SCAN_WARPS * WC;
+  const size_t smem = (size_t)2 * SCAN_CHUNK * (2 * a.N + COLS + 2) * sizeof(float);
   if (smem > 48 * 1024) return FT_ERR_SHAPE;
-  const dim3 grid((a.P + SCAN_COLS - 1) / SCAN_COLS, a.heads, S);
-  cudaError_t e = launch_pdl(ssd_scan_kernel<AT, NPL>, grid, dim3(SCAN_WARPS * 32), smem, stream, a);
+  a.vec = !(a.P % (WC % 4 == 0 ? 4 : 2)) && !(a.slot_stride % 4) && !((uintptr_t)a.state & 15);
+  const dim3 grid((a.P + COLS - 1) / COLS, a.heads, S);
+  cudaError_t e = launch_pdl(ssd_scan_kernel<AT, NPL, WC>, grid, dim3(SCAN_THREADS), smem, stream, a);
   return e == cudaSuccess ? FT_OK : (int)e;
 }
 
-template <typename AT, int NPL>
-static int launch_delta(const DeltaArgs& a, int S, cudaStream_t stream) {
-  const size_t smem = (size_t)(SCAN_CHUNK * (2 * a.D + SCAN_COLS) + 3 * SCAN_CHUNK) * sizeof(float);
+template <typename AT, int NPL, int WC>
+static int launch_delta(DeltaArgs a, int S, cudaStream_t stream) {
+  constexpr int COLS = SCAN_WARPS * WC;
+  const size_t smem = (size_t)2 * SCAN_CHUNK * (2 * a.D + COLS + 2) * sizeof(float);
   if (smem > 48 * 1024) return FT_ERR_SHAPE;
-  const dim3 grid((a.P + SCAN_COLS - 1) / SCAN_COLS, a.heads, S);
-  cudaError_t e = launch_pdl(delta_scan_kernel<AT, NPL>, grid, dim3(SCAN_WARPS * 32), smem, stream, a);
+  a.vec = !(a.P % (WC % 4 == 0 ? 4 : 2)) && !(a.slot_stride % 4) && !((uintptr_t)a.state & 15);
+  const dim3 grid((a.P + COLS - 1) / COLS, a.heads, S);
+  cudaError_t e = launch_pdl(delta_scan_kernel<AT, NPL, WC>, grid, dim3(SCAN_THREADS), smem, stream, a);
   return e == cudaSuccess ? FT_OK : (int)e;
 }
 
@@ -416,7 +737,24 @@ int ft_conv_silu(const void* x, long long ldx, void* out, long long ldo, const f
   if (C <= 0 || taps < 1) return FT_ERR_SHAPE;
   ConvArgs a{x, out, w, bias, state, token_seg, seg_slot, seg_q_start, ldx, ldo, slot_stride, C, taps};
   const int cb = (C + 127) / 128;
-  FT_DISPATCH(dtype, AT, launch_pdl(conv_silu_kernel<AT>, dim3(T, cb), dim3(128), 0, stream, a));
+  if (taps > CONV_MAX_TAPS) {
+    FT_DISPATCH(dtype, AT, launch_pdl(conv_silu_long_kernel<AT>, dim3(T, cb), dim3(128), 0, stream, a));
+  } else {
+    // many tokens: a thread walks 8 of them with its inputs in registers; few: a thread a token
+    const bool many = T >= 1024;
+    const dim3 rows(many ? (T + 7) / 8 : T);
+    const bool pairs = dtype == FT_DTYPE_BF16 && !(C & 1) && !(ldx & 1) && !(ldo & 1) && !((uintptr_t)x & 3) &&
+                       !((uintptr_t)out & 3);
+    if (pairs) {
+      const dim3 grid(rows.x, (C / 2 + 127) / 128);
+      if (many) launch_pdl(conv_silu_kernel<__nv_bfloat16, 2, 8>, grid, dim3(128), 0, stream, a, T);
+      else launch_pdl(conv_silu_kernel<__nv_bfloat16, 2, 1>, grid, dim3(128), 0, stream, a, T);
+    } else if (many) {
+      FT_DISPATCH(dtype, AT, launch_pdl(conv_silu_kernel<AT, 1, 8>, dim3(rows.x, cb), dim3(128), 0, stream, a, T));
+    } else {
+      FT_DISPATCH(dtype, AT, launch_pdl(conv_silu_kernel<AT, 1, 1>, dim3(rows.x, cb), dim3(128), 0, stream, a, T));
+    }
+  }
   FT_LAUNCH_CHECK();
   if (taps > 1) {
     FT_DISPATCH(dtype, AT, launch_pdl(conv_state_kernel<AT>, dim3(S, cb), dim3(128), 0, stream, a));
@@ -431,13 +769,14 @@ int ft_ssd_scan(const void* xbc, long long ld, const void* dt, long long ld_dt, 
                 int dtype, cudaStream_t stream) {
   if (S <= 0) return FT_OK;
   if (heads <= 0 || P <= 0 || N <= 0 || N > 256 || G <= 0 || heads % G) return FT_ERR_SHAPE;
-  SsdArgs a{xbc, dt, dt_bias, A_log, D, state, y, seg_slot, seg_q_start, ld, ld_dt, slot_stride, heads, P, N, G};
+  SsdArgs a{xbc, dt, dt_bias, A_log, D, state, y, seg_slot, seg_q_start, ld, ld_dt, slot_stride, heads, P, N, G, 0};
   int rc = FT_OK;
+  const bool narrow = narrow_warps(P, heads, S);
   FT_DISPATCH(dtype, AT, {
-    if (N <= 32) rc = launch_ssd<AT, 1>(a, S, stream);
-    else if (N <= 64) rc = launch_ssd<AT, 2>(a, S, stream);
-    else if (N <= 128) rc = launch_ssd<AT, 4>(a, S, stream);
-    else rc = launch_ssd<AT, 8>(a, S, stream);
+    if (N <= 32) rc = narrow ? launch_ssd<AT, 1, NARROW_WC>(a, S, stream) : launch_ssd<AT, 1, 8>(a, S, stream);
+    else if (N <= 64) rc = narrow ? launch_ssd<AT, 2, NARROW_WC>(a, S, stream) : launch_ssd<AT, 2, 8>(a, S, stream);
+    else if (N <= 128) rc = narrow ? launch_ssd<AT, 4, NARROW_WC>(a, S, stream) : launch_ssd<AT, 4, 8>(a, S, stream);
+    else rc = narrow ? launch_ssd<AT, 8, NARROW_WC>(a, S, stream) : launch_ssd<AT, 8, 8>(a, S, stream);
   });
   if (rc != FT_OK) return rc;
   FT_LAUNCH_CHECK();
@@ -451,13 +790,14 @@ int ft_delta_scan(const void* qkv, long long ld, const void* beta, const void* d
   if (S <= 0) return FT_OK;
   if (heads <= 0 || P <= 0 || D <= 0 || D > 256 || G <= 0 || heads % G) return FT_ERR_SHAPE;
   DeltaArgs a{qkv, beta, decay, dt_bias, A_log, state, o, seg_slot, seg_q_start, ld, ld_gate, slot_stride,
-              heads, P, D, G, unit_eps, q_scale};
+              heads, P, D, G, unit_eps, q_scale, 0};
   int rc = FT_OK;
+  const bool narrow = narrow_warps(P, heads, S);
   FT_DISPATCH(dtype, AT, {
-    if (D <= 32) rc = launch_delta<AT, 1>(a, S, stream);
-    else if (D <= 64) rc = launch_delta<AT, 2>(a, S, stream);
-    else if (D <= 128) rc = launch_delta<AT, 4>(a, S, stream);
-    else rc = launch_delta<AT, 8>(a, S, stream);
+    if (D <= 32) rc = narrow ? launch_delta<AT, 1, NARROW_WC>(a, S, stream) : launch_delta<AT, 1, 8>(a, S, stream);
+    else if (D <= 64) rc = narrow ? launch_delta<AT, 2, NARROW_WC>(a, S, stream) : launch_delta<AT, 2, 8>(a, S, stream);
+    else if (D <= 128) rc = narrow ? launch_delta<AT, 4, NARROW_WC>(a, S, stream) : launch_delta<AT, 4, 8>(a, S, stream);
+    else rc = narrow ? launch_delta<AT, 8, NARROW_WC>(a, S, stream) : launch_delta<AT, 8, 8>(a, S, stream);
   });
   if (rc != FT_OK) return rc;
   FT_LAUNCH_CHECK();
@@ -469,6 +809,30 @@ int ft_gated_norm(const float* y, const void* z, long long ldz, const float* wei
   if (T <= 0) return FT_OK;
   if (width <= 0 || groups <= 0 || width % groups || weight_len <= 0) return FT_ERR_SHAPE;
   const long long items = (long long)T * groups;
+  const int size = width / groups;
+  const bool vec = !(size & 3) && !(weight_len & 3) && !(ldz & 3) && !((uintptr_t)y & 15) && !((uintptr_t)z & 15) &&
+                   !((uintptr_t)weight & 15) && !((uintptr_t)out & 15);
+  if (vec && size <= 16 * 32) {
+    FT_DISPATCH(dtype, AT, launch_pdl(gated_norm_vec_kernel<AT, 32, 4>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream,
+                                      y, (const AT*)z, ldz, weight, weight_len, (AT*)out, T, width, groups, eps,
+                                      gate_first));
+    FT_LAUNCH_CHECK();
+    return FT_OK;
+  }
+  if (vec && size <= 16 * 128) {
+    FT_DISPATCH(dtype, AT, launch_pdl(gated_norm_vec_kernel<AT, 128, 4>, dim3((unsigned)items), dim3(128), 0, stream, y,
+                                      (const AT*)z, ldz, weight, weight_len, (AT*)out, T, width, groups, eps,
+                                      gate_first));
+    FT_LAUNCH_CHECK();
+    return FT_OK;
+  }
+  if (vec && size <= 64 * 128) {
+    FT_DISPATCH(dtype, AT, launch_pdl(gated_norm_vec_kernel<AT, 128, 16>, dim3((unsigned)items), dim3(128), 0, stream, y,
+                                      (const AT*)z, ldz, weight, weight_len, (AT*)out, T, width, groups, eps,
+                                      gate_first));
+    FT_LAUNCH_CHECK();
+    return FT_OK;
+  }
   const unsigned blocks = (unsigned)((items + 3) / 4);
   FT_DISPATCH(dtype, AT, launch_pdl(gated_norm_kernel<AT>, dim3(blocks), dim3(128), 0, stream, y, (const AT*)z, ldz,
                                     weight, weight_len, (AT*)out, T, width, groups, eps, gate_first));

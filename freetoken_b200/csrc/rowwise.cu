@@ -269,7 +269,19 @@ __global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ x, lon
 // mult * rms(z) * (w [+1]).  With a second weight the new residual row is normed once more
 // in the same pass and leaves as the next sublayer's input.  A block owns a token; z, then the
 // new residual row, stay in shared memory between the passes.
-template <typename AT>
+__device__ __forceinline__ void store4f(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4f(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+constexpr int NORM_ADD_KEEP = 8;   // groups of 4 elements a thread keeps between the passes
+
+// VEC: rows of up to 4 * 256 * NORM_ADD_KEEP elements, a multiple of 4, every row 16-byte (bfloat16: 8-byte)
+// aligned: each row is read once, in 16-byte pieces, and stays in registers between the passes.
+template <typename AT, bool VEC>
 __global__ void __launch_bounds__(256)
 norm_add_kernel(const AT* __restrict__ branch, int k, const float* __restrict__ part_scale,
                 const float* __restrict__ weight, int plus_one, float eps, float mult,
@@ -281,7 +293,59 @@ norm_add_kernel(const AT* __restrict__ branch, int k, const float* __restrict__ 
   const int t = blockIdx.x;
   const AT* b = branch + (size_t)t * k * H;
   float* r = residual + (size_t)t * H;
-  float ss = 0.f;
+  const float one = plus_one ? 1.f : 0.f;
+  const float one2 = next_plus_one ? 1.f : 0.f;
+  float ss = 0.f, ss2 = 0.f;
+  if constexpr (VEC) {
+    float4 keep[NORM_ADD_KEEP];
+    const int groups = H >> 2;
+#pragma unroll
+    for (int j = 0; j < NORM_ADD_KEEP; ++j) {
+      const int gi = threadIdx.x + j * 256;
+      if (gi < groups) {
+        float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; q < k; ++q) {
+          const float4 v = load4f(b + (size_t)q * H + 4 * gi);
+          if (part_scale) {
+            const float s = part_scale[q];
+            z.x = fmaf(s, v.x, z.x); z.y = fmaf(s, v.y, z.y); z.z = fmaf(s, v.z, z.z); z.w = fmaf(s, v.w, z.w);
+          } else {
+            z.x += v.x; z.y += v.y; z.z += v.z; z.w += v.w;
+          }
+        }
+        keep[j] = z;
+        ss = fmaf(z.x, z.x, ss); ss = fmaf(z.y, z.y, ss); ss = fmaf(z.z, z.z, ss); ss = fmaf(z.w, z.w, ss);
+      }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < NORM_ADD_KEEP; ++j) {
+      const int gi = threadIdx.x + j * 256;
+      if (gi < groups) {
+        const float4 w = load4f(weight + 4 * gi), x0 = load4f(r + 4 * gi), z = keep[j];
+        const float4 x = make_float4(x0.x + mult * (z.x * inv * (w.x + one)), x0.y + mult * (z.y * inv * (w.y + one)),
+                                     x0.z + mult * (z.z * inv * (w.z + one)), x0.w + mult * (z.w * inv * (w.w + one)));
+        store4f(r + 4 * gi, x);
+        keep[j] = x;
+        ss2 = fmaf(x.x, x.x, ss2); ss2 = fmaf(x.y, x.y, ss2); ss2 = fmaf(x.z, x.z, ss2); ss2 = fmaf(x.w, x.w, ss2);
+      }
+    }
+    if (!next_weight) return;
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.0f / sqrtf(ss2 / (float)H + next_eps);
+    AT* o = next_out + (size_t)t * H;
+#pragma unroll
+    for (int j = 0; j < NORM_ADD_KEEP; ++j) {
+      const int gi = threadIdx.x + j * 256;
+      if (gi < groups) {
+        const float4 w = load4f(next_weight + 4 * gi), x = keep[j];
+        store4f(o + 4 * gi, make_float4(x.x * inv2 * (w.x + one2), x.y * inv2 * (w.y + one2), x.z * inv2 * (w.z + one2),
+                                        x.w * inv2 * (w.w + one2)));
+      }
+    }
+    return;
+  } else {
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float z = 0.f;
     for (int j = 0; j < k; ++j) {
@@ -293,8 +357,6 @@ norm_add_kernel(const AT* __restrict__ branch, int k, const float* __restrict__ 
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)H + eps);
-  const float one = plus_one ? 1.f : 0.f;
-  float ss2 = 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     const float x = r[i] + mult * (row[i] * inv * (weight[i] + one));
     r[i] = x;
@@ -304,9 +366,9 @@ norm_add_kernel(const AT* __restrict__ branch, int k, const float* __restrict__ 
   if (!next_weight) return;
   ss2 = block_sum(ss2, scratch);
   const float inv2 = 1.0f / sqrtf(ss2 / (float)H + next_eps);
-  const float one2 = next_plus_one ? 1.f : 0.f;
   AT* o = next_out + (size_t)t * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<AT>(row[i] * inv2 * (next_weight[i] + one2));
+  }
 }
 
 // out[t, :] = sum_j s_j * parts[t, j, :]   (float32 sum, ascending j)
@@ -446,10 +508,19 @@ int ft_norm_add(const void* branch, int k, const float* part_scale, const float*
                 void* next_out, int T, int H, int dtype, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   if (k <= 0 || H <= 0 || H > 12288) return FT_ERR_SHAPE;
-  FT_DISPATCH(dtype, AT,
-              (launch_pdl(norm_add_kernel<AT>, dim3(T), dim3(256), (size_t)H * sizeof(float), stream,
-                          (const AT*)branch, k, part_scale, weight, plus_one, eps, mult, residual, next_weight,
-                          next_plus_one, next_eps, (AT*)next_out, H)));
+  const bool vec = !(H & 3) && H <= 4 * 256 * NORM_ADD_KEEP && !((uintptr_t)branch & 15) && !((uintptr_t)weight & 15) &&
+                   !((uintptr_t)residual & 15) && !((uintptr_t)next_weight & 15) && !((uintptr_t)next_out & 15);
+  if (vec) {
+    FT_DISPATCH(dtype, AT,
+                (launch_pdl(norm_add_kernel<AT, true>, dim3(T), dim3(256), 0, stream, (const AT*)branch, k, part_scale,
+                            weight, plus_one, eps, mult, residual, next_weight, next_plus_one, next_eps,
+                            (AT*)next_out, H)));
+  } else {
+    FT_DISPATCH(dtype, AT,
+                (launch_pdl(norm_add_kernel<AT, false>, dim3(T), dim3(256), (size_t)H * sizeof(float), stream,
+                            (const AT*)branch, k, part_scale, weight, plus_one, eps, mult, residual, next_weight,
+                            next_plus_one, next_eps, (AT*)next_out, H)));
+  }
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

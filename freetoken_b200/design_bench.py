@@ -124,8 +124,6 @@ def measure_model(config: Dict[str, Any], a, seed: int = 0) -> Dict[str, Any]:
     per = max(1, 8192 // a.context)
     for i in range(0, batch, per):
         engine.step([StepEntry(r, rng.integers(0, V, a.context).tolist(), []) for r in ids[i:i + per]])
-    cache_bytes_per_token = sum(t.numel() * t.element_size() // (t.shape[1 + g.need.page_axis] * page)
-                                for t, g in zip(engine.storage.paged, engine.cache.paged_groups))
     for b in (batch, 1):
         live = ids[:b]
 
@@ -136,7 +134,12 @@ def measure_model(config: Dict[str, Any], a, seed: int = 0) -> Dict[str, Any]:
         for _ in range(max(3, a.warmup)):
             decode_once()
         ms = _timed(decode_once, a.steps)
-        nbytes = engine.weight_bytes + b * engine.length(live[0]) * cache_bytes_per_token
+        # a windowed group reads no more than its window; a request's state rows are read and written
+        held = sum(min(engine.length(live[0]), g.need.window or engine.length(live[0])) * (
+            t.numel() * t.element_size() // (t.shape[1 + g.need.page_axis] * page))
+            for t, g in zip(engine.storage.paged, engine.cache.paged_groups))
+        state_bytes = sum(2 * t[:, 0].numel() * t.element_size() for t in engine.storage.state)
+        nbytes = engine.weight_bytes + b * (held + state_bytes)
         out[f"decode_b{b}"] = {"ms": round(ms, 4), "tokens_per_s": round(b / (ms / 1e3)),
                                "bytes_per_step": nbytes, "gbs": round(nbytes / (ms / 1e3) / 1e9, 1),
                                "graph_replays": engine.graph_replays}

@@ -87,7 +87,7 @@ def segments(lens, slots):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
-@pytest.mark.parametrize("taps,bias", [(1, True), (2, False), (4, True), (5, False)])
+@pytest.mark.parametrize("taps,bias", [(1, True), (2, False), (4, True), (5, False), (11, True)])
 def test_conv_silu_carries_its_inputs(dtype, taps, bias):
     """Two requests fed in segments of 1 to 9 tokens that interleave, in slots 2 and 0 of rows that
     are wider than the convolution's state: every output equals the convolution over the whole
@@ -180,18 +180,25 @@ def test_delta_scan_in_segments(dtype, heads, G, D, P):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
-def test_gated_norm_both_orders(dtype):
+@pytest.mark.parametrize("width,cases", [
+    (60, ((4, 60, True), (1, 60, True), (5, 12, False))),            # parts of 15, 60, 12 values: a warp each
+    (1536, ((1, 1536, True), (12, 128, False), (3, 1536, True))),    # a block a part; a warp a part
+    (4100, ((1, 4100, True), (5, 820, False))),                      # rows kept in 16 pieces a thread
+    (9004, ((1, 9004, True),)),                                      # longer than a thread block keeps
+    (90, ((2, 45, False),)),                                         # an odd part: one value at a time
+])
+def test_gated_norm_both_orders(dtype, width, cases):
     from freetoken_b200.csrc import ops
     torch.manual_seed(5)
-    T, width = 7, 60
+    T = 7
     y = torch.randn(T, width, device="cuda") * 3
-    z = torch.randn(T, width + 4).to(DTYPES[dtype]).cuda()
+    z = torch.randn(T, width + 8).to(DTYPES[dtype]).cuda()
     tol = 1e-5 if dtype == "float32" else 2e-2
-    for groups, wlen, first in ((4, 60, True), (1, 60, True), (5, 12, False)):
+    for groups, wlen, first in cases:
         w = (torch.rand(wlen) + 0.5).cuda()
         out = torch.empty(T, width, dtype=DTYPES[dtype], device="cuda")
-        ops.gated_norm(y, z[:, 4:], w, out, groups, 1e-3, first)
-        gate = plain.silu(z[:, 4:].double().cpu())
+        ops.gated_norm(y, z[:, 8:], w, out, groups, 1e-3, first)
+        gate = plain.silu(z[:, 8:].double().cpu())
         v = y.double().cpu() * gate if first else y.double().cpu()
         v = plain.rms(v.view(T, groups, width // groups), 1e-3).reshape(T, width) * w.double().cpu().repeat(width // wlen)
         want = v if first else v * gate
