@@ -67,8 +67,9 @@ TN_B: Dict = model(320, 128, 2e-6, 1.0, [
     parallel(left(2, 2, 128, 128, 130, 128), right(8, 16, 16, 4, 5, 8), 0.6, 0.9, dense(192)),
 ])
 
-# delta layers only first (no paged cache before the last layer); no rotation; one expert of one
-TN_C: Dict = model(97, 72, 1e-4, 0.35, [
+# delta layers only first (no paged cache before the last layer); no rotation; one expert of one;
+# a width that is no multiple of 4 (no 16-byte pieces anywhere along a row of the residual)
+TN_C: Dict = model(97, 70, 1e-4, 0.35, [
     delta(3, 1, 20, 28, 5, moe(1, 1, 30, 0.5)),
     delta(6, 6, 8, 12, 2, dense(100)),
     parallel(left(6, 3, 16, 40, 33, 0), right(3, 24, 33, 3, 2, 3), 1.0, 1.0),
