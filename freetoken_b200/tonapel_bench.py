@@ -46,7 +46,7 @@ def tonapel_config(s: Dict[str, int]) -> Dict[str, Any]:
     dense = {"kind": "dense", "ff": s["ff"] * 2 // 3 // 128 * 128}
     moe = {"kind": "moe", "expert": {"ff": inter, "limit": 7.0}, "router": {"experts": s["experts"], "top": s["top"]}}
     return {"architecture": "Tonapel", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
-            "residual_mult": 0.5,
+            "residual_mult": 0.7,
             "layers": [{"type": "parallel", "mixer": par, "mlp": dense}, {"type": "delta", "mixer": dl, "mlp": moe},
                        {"type": "parallel", "mixer": par, "mlp": moe}, {"type": "delta", "mixer": dl, "mlp": dense}]}
 

@@ -179,6 +179,17 @@ def expert(h, p, W, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ W[p + "down"].T
 
 
+def route_margin(h, p, W, c):
+    """Per token: how far the last chosen logit lies above the first one not chosen (inf when all
+    experts are chosen)."""
+    z = h @ W[p + "router"].T
+    top = c["router"]["top"]
+    if top >= z.shape[1]:
+        return torch.full((z.shape[0],), float("inf"), dtype=z.dtype)
+    best = torch.topk(z, top + 1, dim=-1).values
+    return best[:, top - 1] - best[:, top]
+
+
 def moe_ff(h, p, W, c, ids=None):
     own_ids, _ = route(h, p, W, c)
     ids = own_ids if ids is None else ids
@@ -192,9 +203,10 @@ def moe_ff(h, p, W, c, ids=None):
     return out
 
 
-def forward(cfg, W, tokens, layer_dump=None, expert_ids=None):
+def forward(cfg, W, tokens, layer_dump=None, expert_ids=None, margins=None):
     """Logits ``[T, vocab]`` of one sequence; ``layer_dump`` collects the residual stream after
-    every layer; ``expert_ids`` (per routed layer, ``[T, top]``) replaces the router's own choice."""
+    every layer; ``expert_ids`` (per routed layer, ``[T, top]``) replaces the router's own choice;
+    ``margins`` collects every routed layer's :func:`route_margin`."""
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
     x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     routed = 0
@@ -216,6 +228,8 @@ def forward(cfg, W, tokens, layer_dump=None, expert_ids=None):
             else:
                 ids = None if expert_ids is None else expert_ids[routed]
                 routed += 1
+                if margins is not None:
+                    margins.append(route_margin(h, p + "mlp.", W, mlp))
                 f = moe_ff(h, p + "mlp.", W, mlp, ids)
             x = x + m * norm(f, W[p + "norm2b"], eps)
         if layer_dump is not None:

@@ -465,15 +465,21 @@ def test_greedy_generation_through_the_scheduler(models, which, dtype):
     prompts = [tn.tokens(70 + i, n, config["vocab"]) for i, n in enumerate((3, 30, 11, 1, 47))]
     out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
     tie = 1e-4 if dtype == "float32" else 8e-2
+    route_tie = 5e-2         # bfloat16: two router logits this close may be chosen the other way round
     ties = 0
     for prompt, result in zip(prompts, out):
         seq = list(prompt)
         assert len(result["token_ids"]) == 12
         for token in result["token_ids"]:
-            logits = plain.forward(config, state, seq)[-1]
+            margins = []
+            logits = plain.forward(config, state, seq, margins=margins)[-1]
             if token != int(logits.argmax()):
-                assert float(logits.max() - logits[token]) < tie, (dtype, len(seq), token, int(logits.argmax()))
+                margin = min((float(m.min()) for m in margins), default=float("inf"))
+                close = float(logits.max() - logits[token]) < tie or (dtype == "bfloat16" and margin < route_tie)
+                assert close, (dtype, len(seq), token, int(logits.argmax()), float(logits.max() - logits[token]), margin)
                 ties += 1
+                if margin < route_tie:
+                    break            # another expert somewhere in the sequence: what follows is another sequence
             seq.append(int(token))
     assert ties == 0 if dtype == "float32" else ties <= 4
     if dtype == "bfloat16":

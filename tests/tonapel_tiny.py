@@ -61,10 +61,10 @@ TN_A: Dict = model(150, 40, 1e-5, 0.7, [
 # sizes the tensor-core attention kernels take (32, 64, 128; keys and values alike), pages of 64,
 # windows shorter than, equal to and longer than a page
 TN_B: Dict = model(320, 128, 2e-6, 1.0, [
-    parallel(left(4, 2, 64, 64, 100, 32), right(4, 32, 64, 2, 4, 2), 0.8, 1.1, dense(256)),
+    parallel(left(4, 2, 64, 64, 100, 32), right(4, 32, 64, 2, 4, 2), 0.75, 1.1, dense(256)),
     delta(4, 2, 64, 64, 4, moe(8, 2, 64, 7.0)),
     parallel(left(8, 1, 32, 32, 64, 16, base=5000.0), right(2, 64, 128, 1, 3, 1), 1.0, 0.4, moe(6, 1, 48, 1.5)),
-    parallel(left(2, 2, 128, 128, 130, 128), right(8, 16, 16, 4, 5, 8), 0.6, 0.9, dense(192)),
+    parallel(left(2, 2, 128, 128, 130, 128), right(8, 16, 16, 4, 5, 8), 0.6, 0.95, dense(192)),
 ])
 
 # delta layers only first (no paged cache before the last layer); no rotation; one expert of one;
