@@ -152,7 +152,7 @@ def test_ssd_scan_in_segments(dtype, heads, P, N, G):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
-@pytest.mark.parametrize("heads,G,D,P", [(4, 2, 12, 10), (2, 2, 40, 36), (4, 1, 128, 64), (3, 3, 8, 70)])
+@pytest.mark.parametrize("heads,G,D,P", [(4, 2, 12, 10), (2, 2, 40, 36), (4, 1, 128, 64), (3, 3, 8, 70), (2, 1, 200, 16)])
 def test_delta_scan_in_segments(dtype, heads, G, D, P):
     from freetoken_b200.csrc import ops
     torch.manual_seed(D)
